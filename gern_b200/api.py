@@ -1,0 +1,194 @@
+"""ctypes binding of include/gern_b200.h.  Device entry points take torch CUDA tensors (used only
+as owners of device memory); `_host` entry points take numpy arrays or CPU torch tensors."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import numpy as np
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libgern_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m gern_b200.build` (there is no CPU or "
+        "PyTorch fallback for the gern_b200 kernels)")
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_i64 = ctypes.c_int64
+_vp = ctypes.c_void_p
+_int = ctypes.c_int
+
+# name -> argtypes (after the leading ctx pointer); every function returns int unless noted.
+SIGNATURES = {
+    "gb200_ctx_create": None,
+    "gb200_ctx_destroy": None,
+    "gb200_device_sync": None,
+    "gb200_last_error_string": None,
+    "gb200_version": None,
+    "gb200_launch_count": None,
+    "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
+    "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
+    "gb200_softmax_rows_f32": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
+    "gb200_blur3x3_f32": [_vp, _i64, _i64, _i64, _vp, _i64, _vp],
+    "gb200_blur3x3_f32_variant": [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _int],
+    "gb200_blur3x3_f32_band": [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp],
+    "gb200_attention_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
+                             ctypes.c_float, _vp],
+    "gb200_gemm_f32_host": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int],
+    "gb200_gemm_bf16_host": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64],
+    "gb200_softmax_rows_f32_host": [_vp, _i64, _vp, _i64, _i64, _i64],
+    "gb200_blur3x3_f32_host": [_vp, _i64, _i64, _i64, _vp, _i64],
+    "gb200_attention_bf16_host": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
+                                  ctypes.c_float],
+}
+
+lib.gb200_ctx_create.argtypes = [_int, ctypes.POINTER(_vp)]
+lib.gb200_ctx_destroy.argtypes = [_vp]
+lib.gb200_device_sync.argtypes = [_vp]
+lib.gb200_last_error_string.restype = ctypes.c_char_p
+lib.gb200_version.restype = ctypes.c_char_p
+lib.gb200_launch_count.argtypes = [_vp]
+lib.gb200_launch_count.restype = _i64
+for _name, _args in SIGNATURES.items():
+    if _args is not None and hasattr(lib, _name):
+        getattr(lib, _name).argtypes = [_vp] + _args
+        getattr(lib, _name).restype = _int
+
+
+class GernB200Error(RuntimeError):
+    def __init__(self, code: int, what: str):
+        self.code = code
+        msg = lib.gb200_last_error_string().decode(errors="replace")
+        super().__init__(f"{what} failed with status {code}: {msg}")
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise GernB200Error(rc, what)
+
+
+def _ptr(t) -> int:
+    """Address of a torch tensor's / numpy array's first element (None -> NULL)."""
+    if t is None:
+        return None
+    if isinstance(t, np.ndarray):
+        return t.ctypes.data
+    return t.data_ptr()
+
+
+def _stream(stream) -> int | None:
+    if stream is None:
+        return None
+    return getattr(stream, "cuda_stream", stream)
+
+
+def _ld(t) -> int:
+    if isinstance(t, np.ndarray):
+        assert t.strides[1] == t.itemsize, "rows must be contiguous"
+        return t.strides[0] // t.itemsize
+    assert t.stride(1) == 1, "rows must be contiguous"
+    return t.stride(0)
+
+
+class Context:
+    """Owner of a gb200_ctx (one per process and device)."""
+
+    def __init__(self, device: int = 0):
+        h = _vp()
+        _check(lib.gb200_ctx_create(int(device), ctypes.byref(h)), "gb200_ctx_create")
+        self.handle = h
+        self.device = device
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            lib.gb200_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sync(self) -> None:
+        _check(lib.gb200_device_sync(self.handle), "gb200_device_sync")
+
+    def launch_count(self) -> int:
+        return int(lib.gb200_launch_count(self.handle))
+
+    # ---- device entry points (torch CUDA tensors) ----
+    def gemm_f32(self, A, B, C, accumulate=False, stream=None):
+        M, K = A.shape
+        N = B.shape[1]
+        _check(lib.gb200_gemm_f32(self.handle, _ptr(A), _ld(A), _ptr(B), _ld(B), _ptr(C), _ld(C), M, N, K,
+                                  int(bool(accumulate)), _stream(stream)), "gb200_gemm_f32")
+
+    def gemm_bf16(self, A, Bt, C, stream=None):
+        """A: (M,K) bf16; Bt: (N,K) bf16 (column-major B); C: (M,N) bf16."""
+        M, K = A.shape
+        N = Bt.shape[0]
+        _check(lib.gb200_gemm_bf16(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N,
+                                   K, _stream(stream)), "gb200_gemm_bf16")
+
+    def softmax_rows(self, x, out, stream=None):
+        rows, cols = x.shape
+        _check(lib.gb200_softmax_rows_f32(self.handle, _ptr(x), _ld(x), _ptr(out), _ld(out), rows, cols,
+                                          _stream(stream)), "gb200_softmax_rows_f32")
+
+    def blur3x3(self, x, out, stream=None, variant=None):
+        rows, cols = x.shape
+        if variant is None:
+            _check(lib.gb200_blur3x3_f32(self.handle, _ptr(x), _ld(x), rows, cols, _ptr(out), _ld(out),
+                                         _stream(stream)), "gb200_blur3x3_f32")
+        else:
+            _check(lib.gb200_blur3x3_f32_variant(self.handle, _ptr(x), _ld(x), rows, cols, _ptr(out),
+                                                 _ld(out), _stream(stream), int(variant)),
+                   "gb200_blur3x3_f32_variant")
+
+    def blur3x3_band(self, x, halo, out, stream=None, halo_ptr=None, halo_ld=None):
+        """x: this rank's band; halo: tensor with the 2 rows that follow it (or None)."""
+        rows, cols = x.shape
+        hp = halo_ptr if halo_ptr is not None else _ptr(halo)
+        hl = halo_ld if halo_ld is not None else (_ld(halo) if halo is not None else 0)
+        _check(lib.gb200_blur3x3_f32_band(self.handle, _ptr(x), _ld(x), rows, cols, hp, hl, _ptr(out),
+                                          _ld(out), _stream(stream)), "gb200_blur3x3_f32_band")
+
+    def attention_bf16(self, Q, K, V, O, scale, stream=None):
+        nq, d = Q.shape
+        nkv = K.shape[0]
+        _check(lib.gb200_attention_bf16(self.handle, _ptr(Q), _ld(Q), _ptr(K), _ld(K), _ptr(V), _ld(V),
+                                        _ptr(O), _ld(O), nq, nkv, d, ctypes.c_float(scale),
+                                        _stream(stream)), "gb200_attention_bf16")
+
+    # ---- host entry points (numpy arrays / CPU tensors) ----
+    def gemm_f32_host(self, A, B, C, accumulate=False):
+        M, K = A.shape
+        N = B.shape[1]
+        _check(lib.gb200_gemm_f32_host(self.handle, _ptr(A), _ld(A), _ptr(B), _ld(B), _ptr(C), _ld(C), M,
+                                       N, K, int(bool(accumulate))), "gb200_gemm_f32_host")
+
+    def gemm_bf16_host(self, A, Bt, C):
+        M, K = A.shape
+        N = Bt.shape[0]
+        _check(lib.gb200_gemm_bf16_host(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C),
+                                        M, N, K), "gb200_gemm_bf16_host")
+
+    def softmax_rows_host(self, x, out):
+        rows, cols = x.shape
+        _check(lib.gb200_softmax_rows_f32_host(self.handle, _ptr(x), _ld(x), _ptr(out), _ld(out), rows,
+                                               cols), "gb200_softmax_rows_f32_host")
+
+    def blur3x3_host(self, x, out):
+        rows, cols = x.shape
+        _check(lib.gb200_blur3x3_f32_host(self.handle, _ptr(x), _ld(x), rows, cols, _ptr(out), _ld(out)),
+               "gb200_blur3x3_f32_host")
+
+    def attention_bf16_host(self, Q, K, V, O, scale):
+        nq, d = Q.shape
+        nkv = K.shape[0]
+        _check(lib.gb200_attention_bf16_host(self.handle, _ptr(Q), _ld(Q), _ptr(K), _ld(K), _ptr(V),
+                                             _ld(V), _ptr(O), _ld(O), nq, nkv, d, ctypes.c_float(scale)),
+               "gb200_attention_bf16_host")

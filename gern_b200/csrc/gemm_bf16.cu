@@ -1,0 +1,292 @@
+// bf16 x bf16 -> fp32 (TMEM) -> bf16 matrix multiply on the sm_100a tensor cores.
+//
+// C[M,N] = A[M,K] * B[K,N] with A row-major and B column-major (both K-contiguous), the
+// operator that annot::MatrixMultiply describes (gernels/mm/gern_annot/functions.h:7-60).  The
+// reference's schedule for it (gernels/mm/kernel_10.cu:108-131) stages 32x32 tiles through
+// shared memory with cooperative copies and block barriers and computes on the fp32 pipe,
+// writing C back every K tile (gernels/mm/bench.cu:18-41).  This kernel keeps the same tile
+// structure -- block tile of C, Reduce over K tiles, operands staged in shared memory -- and
+// maps it to Blackwell:
+//   * a persistent CTA per SM walks 128x256 tiles of C;
+//   * warp 0 feeds a 4-deep ring of {A 128x64, B 256x64} bf16 stages with TMA
+//     (128-byte swizzle, completion on mbarriers, no multicast);
+//   * warp 1 issues tcgen05.mma (M128 N256 K16, cta_group::1) from shared-memory descriptors
+//     into one of two 256-column fp32 accumulators in TMEM and releases ring slots with
+//     tcgen05.commit;
+//   * warps 2-5 drain the finished accumulator with tcgen05.ld, round to bf16 and store C,
+//     overlapping the next tile's main loop (the other TMEM accumulator).
+// Every wait is bounded; a wait that runs out records a code in the context's status word and
+// the kernel winds down (TMEM is always freed).
+#include "common.cuh"
+
+namespace gb200 {
+
+namespace gemm {
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;              // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;              // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GROUP_M = 16;                       // tile rows per L2 rasterisation group
+}  // namespace gemm
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
+    // Walk tiles in groups of GROUP_M tile-rows, column by column inside a group, so that the
+    // CTAs running at the same time share A panels and B panels in L2.
+    const int per_group = gemm::GROUP_M * tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * gemm::GROUP_M;
+    const int rows_in_group = min(gemm::GROUP_M, tiles_m - first_m);
+    const int r = t - g * per_group;
+    tm = first_m + r % rows_in_group;
+    tn = r / rows_in_group;
+}
+
+__global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
+gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
+                    int64_t ldc, int M, int N, int K, int *status) {
+    using namespace gemm;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    uint64_t *full = bars;                  // [STAGES] TMA -> MMA
+    uint64_t *empty = bars + STAGES;        // [STAGES] MMA -> TMA
+    uint64_t *acc_full = bars + 2 * STAGES;       // [2] MMA -> epilogue
+    uint64_t *acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_base_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, tiles_m, tiles_n, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1, status, 201)) { ok = false; break; }
+                    unsigned char *sa = smem + s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(sa, &tmap_a, kb * BK, tm * BM, &full[s]);
+                    tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, tn * BN, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
+                const int buf = tile_it & 1;
+                const uint32_t acc_ph = (tile_it >> 1) & 1;
+                if (!mbar_wait(&acc_empty[buf], acc_ph ^ 1, status, 202)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[s], ph, status, 203)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = umma_desc_sw128(sa, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(sa + A_BYTES, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) {
+                        // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row
+                        umma_f16_ss(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                    (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(&empty[s]);  // slot is free once these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> registers -> bf16 -> global ----------------
+        const int lane_group = warp & 3;  // TMEM lanes this warp may touch: 32*(warp%4)...
+        uint32_t tile_it = 0;
+        bool ok = true;
+        const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
+            int tm, tn;
+            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            const int buf = tile_it & 1;
+            const uint32_t acc_ph = (tile_it >> 1) & 1;
+            if (!mbar_wait(&acc_full[buf], acc_ph, status, 204)) { ok = false; break; }
+            tc_fence_after();
+            const int row = tm * BM + lane_group * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                                   static_cast<uint32_t>(buf * BN);
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + ch * 32, r);
+                tmem_ld_wait();
+                const int col = tn * BN + ch * 32;
+                if (row < M && col < N) {
+                    __nv_bfloat16 *dst = C + static_cast<int64_t>(row) * ldc + col;
+                    if (vec_ok && col + 32 <= N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 v;
+                            v.x = pack_bf16(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+                            v.y = pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                            v.z = pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                            v.w = pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                            *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Fallback for operands the TMA path cannot take (pitch or base not 16-byte aligned):
+// plain CUDA-core kernel, fp32 accumulate in ascending k.
+__global__ void __launch_bounds__(256)
+gemm_bf16_simple_kernel(const __nv_bfloat16 *__restrict__ A, int64_t lda,
+                        const __nv_bfloat16 *__restrict__ B, int64_t ldb,
+                        __nv_bfloat16 *__restrict__ C, int64_t ldc, int M, int N, int K) {
+    __shared__ float As[16][17], Bs[16][17];
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int m = blockIdx.y * 16 + ty, n = blockIdx.x * 16 + tx;
+    float acc = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += 16) {
+        const int ka = k0 + tx;
+        As[ty][tx] = (m < M && ka < K) ? __bfloat162float(A[static_cast<int64_t>(m) * lda + ka]) : 0.f;
+        const int nb = blockIdx.x * 16 + ty;
+        Bs[ty][tx] = (nb < N && ka < K) ? __bfloat162float(B[static_cast<int64_t>(nb) * ldb + ka]) : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc = fmaf(As[ty][k], Bs[tx][k], acc);
+        __syncthreads();
+    }
+    if (m < M && n < N) C[static_cast<int64_t>(m) * ldc + n] = __float2bfloat16_rn(acc);
+}
+
+int check_gemm_args(const void *A, int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc,
+                    int64_t M, int64_t N, int64_t K, bool b_colmajor);
+
+int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                       void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    using namespace gemm;
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool tc_ok = ctx->encode_tiled && al16(A) && al16(B) && lda % 8 == 0 && ldb % 8 == 0 &&
+                       K > 0;
+    if (!tc_ok) {
+        dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
+        gemm_bf16_simple_kernel<<<grid, 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16 *>(A), lda, static_cast<const __nv_bfloat16 *>(B), ldb,
+            static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K);
+        return after_launch(ctx, "gemm_bf16_simple_kernel");
+    }
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
+                         (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
+                     (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
+    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_bf16_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, ctx->d_status);
+    return after_launch(ctx, "gemm_bf16_tc_kernel");
+}
+
+}  // namespace gb200
+
+using namespace gb200;
+
+extern "C" {
+
+int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                    void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return gemm_bf16_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                         void *C, int64_t ldc, int64_t M, int64_t N, int64_t K) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    const int64_t dk = (K + 7) / 8 * 8, dn = (N + 7) / 8 * 8;
+    rc = stage_reserve(ctx, 0, (size_t)M * dk * 2 + 16);
+    if (rc) return rc;
+    rc = stage_reserve(ctx, 1, (size_t)N * dk * 2 + 16);
+    if (rc) return rc;
+    rc = stage_reserve(ctx, 2, (size_t)M * dn * 2 + 16);
+    if (rc) return rc;
+    cudaStream_t s = ctx->copy_stream[0];
+    if (K > 0) {
+        GB200_CUDA_TRY(cudaMemcpy2DAsync(ctx->stage[0], dk * 2, A, lda * 2, K * 2, M,
+                                         cudaMemcpyHostToDevice, s));
+        GB200_CUDA_TRY(cudaMemcpy2DAsync(ctx->stage[1], dk * 2, B, ldb * 2, K * 2, N,
+                                         cudaMemcpyHostToDevice, s));
+    }
+    rc = gemm_bf16_dispatch(ctx, ctx->stage[0], dk, ctx->stage[1], dk, ctx->stage[2], dn, M, N, K, s);
+    if (rc) return rc;
+    GB200_CUDA_TRY(cudaMemcpy2DAsync(C, ldc * 2, ctx->stage[2], dn * 2, N * 2, M,
+                                     cudaMemcpyDeviceToHost, s));
+    GB200_CUDA_TRY(cudaStreamSynchronize(s));
+    return GB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+/*
+ * gern_b200.h -- C ABI of libgern_b200.so: hand-written sm_100a (B200) kernels for the
+ * fused data-parallel programs that Gern's lowering emits (tiled matrix multiply, row
+ * softmax, the two-stage blur, and the GEMM -> softmax -> GEMM chain).
+ *
+ * The library stands where Gern's generic emitted `__global__ function_N` stands today:
+ * the host function that `Runner::compile` builds (src/codegen/codegen.cpp:31-101 emits the
+ * `extern "C" hook_<fn>(void**)`, src/codegen/runner.cpp:17-52 compiles and dlopens it)
+ * calls one of the entry points below instead of launching an emitted kernel
+ * (src/codegen/codegen.cpp:576-611).  Every entry point takes plain pointers and sizes,
+ * never owns a caller's buffer, never calls exit(), and returns an int status.
+ *
+ * Conventions
+ *   - All matrices are dense with an explicit leading dimension `ld*` counted in elements.
+ *   - "row-major M x K, ld" means element (i,k) lives at ptr[i*ld + k].
+ *   - Device entry points take device pointers valid on the context's device and enqueue
+ *     work on `stream` (a cudaStream_t passed as void*; NULL = the legacy default stream,
+ *     which is what Gern's emitted hook uses).  They do not synchronise.
+ *   - `_host` entry points take host pointers (pinned memory is fastest), copy the operands
+ *     to the device, run the same kernels, copy the result back and return after the result
+ *     is in host memory.
+ *   - Status: 0 = success; negative = failure (see gb200_status).  A human-readable message
+ *     for the calling thread's last failure is returned by gb200_last_error_string().
+ */
+#ifndef GERN_B200_H
+#define GERN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gb200_ctx gb200_ctx;
+
+enum gb200_status {
+    GB200_OK = 0,
+    GB200_ERR_INVALID_ARG = -1,  /* null pointer, negative size, ld smaller than the row, ... */
+    GB200_ERR_CUDA = -2,         /* a CUDA runtime / driver call failed                        */
+    GB200_ERR_UNSUPPORTED = -3,  /* shape or alignment this build has no kernel for            */
+    GB200_ERR_NO_DEVICE = -4,    /* no sm_100 device, or the driver is missing                 */
+    GB200_ERR_TIMEOUT = -5,      /* a bounded device-side wait ran out (kernel reported it)    */
+    GB200_ERR_TOO_LARGE = -6     /* request exceeds a fixed capacity of the entry point        */
+};
+
+/* ---- context -------------------------------------------------------------------------- */
+
+/* Creates a context bound to CUDA device `device`.  The context owns only library scratch:
+ * cached TMA descriptors, the staging buffers of the `_host` entry points and a small status
+ * word.  Replaces the per-launch `cudaGetDeviceProperties` of Gern's hook
+ * (include/gern/codegen/helpers/assert_device_properties.h:15-42): device limits are read
+ * once here. */
+int gb200_ctx_create(int device, gb200_ctx **out);
+int gb200_ctx_destroy(gb200_ctx *ctx);
+/* cudaDeviceSynchronize on the context's device (Gern's callers synchronise implicitly
+ * through cudaMemcpy in MatrixGPU::get(), apps/common/impl/gpu-matrix-const.h:221-225). */
+int gb200_device_sync(gb200_ctx *ctx);
+const char *gb200_last_error_string(void);
+const char *gb200_version(void);
+/* Number of kernels this library has launched on behalf of `ctx` since it was created. */
+int64_t gb200_launch_count(gb200_ctx *ctx);
+
+/* ---- matrix multiply ------------------------------------------------------------------ */
+
+/* fp32 C (+)= A * B, all row-major.  A: M x K (lda), B: K x N (ldb), C: M x N (ldc).
+ * accumulate != 0 adds into C (Gern's leaf does `c += sum`), 0 overwrites C.
+ * Replaces the emitted kernel of gernels/mm/kernel_10.cu:108-131 (copy:
+ * gernels/mm/bench.cu:10-44) and its leaf `matrix_multiply<k_dim>`
+ * (gernels/mm/impl/matrix_multiply.h:50-61); CPU twin gern::impl::matrix_multiply
+ * (test/library/matrix/impl/cpu-matrix.h:196-212). */
+int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
+                   float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
+                   void *stream);
+
+/* bf16 inputs, fp32 accumulate (tcgen05 / TMEM), bf16 output.  A: row-major M x K (lda).
+ * B: column-major K x N, i.e. stored as N rows of K contiguous elements (ldb >= K).
+ * C: row-major M x N (ldc).  Same annotation as annot::MatrixMultiply
+ * (gernels/mm/gern_annot/functions.h:7-60); the reference has no bf16 leaf. */
+int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                    void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream);
+
+/* ---- row softmax ---------------------------------------------------------------------- */
+
+/* out(i,:) = exp(in(i,:) - max_j in(i,j)) / sum_j exp(in(i,j) - max_j in(i,j)), fp32.
+ * One fused pass replacing the five annotated ops MaxRow / SubstractVec / ExpMatrix /
+ * SumRow / DivideVec (apps/common/annot/functions.h:9-173; device code
+ * apps/common/impl/impl.h:7-188; CPU twins test/library/matrix/impl/cpu-matrix.h:134-194). */
+int gb200_softmax_rows_f32(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
+                           int64_t ld_out, int64_t rows, int64_t cols, void *stream);
+
+/* ---- fused two-stage blur ------------------------------------------------------------- */
+
+/* t(i,j) = (in(i,j)+in(i,j+1)+in(i,j+2))/3 ; out(i,j) = (t(i,j)+t(i+1,j)+t(i+2,j))/3 with
+ * out of size (in_rows-2) x (in_cols-2); t never reaches HBM.  Bit-exact with the reference's
+ * cpu_blur_x / cpu_blur_y (apps/blur/blur.cpp:11-25).  Replaces the emitted kernel
+ * apps/blur/blur.cu:19-45 and the leaves blur_x<3>/blur_y<3>
+ * (apps/common/impl/impl.h:190-250; annotations apps/common/annot/functions.h:175-249). */
+int gb200_blur3x3_f32(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
+                      int64_t in_cols, float *out, int64_t out_ld, void *stream);
+
+/* Row-band form used when an image is sharded by rows across GPUs: `in` holds `band_rows`
+ * rows of the band this GPU owns and `halo` holds the 2 rows that follow it (they belong to
+ * the next band; `halo` may point into a peer GPU's memory, it is read with ordinary loads).
+ * Produces band_rows output rows.  With halo == NULL it produces band_rows-2 rows (last band).
+ * No counterpart in the reference, which is single-GPU. */
+int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t band_rows,
+                           int64_t in_cols, const float *halo, int64_t halo_ld, float *out,
+                           int64_t out_ld, void *stream);
+
+/* ---- GEMM -> row softmax -> GEMM chain ------------------------------------------------- */
+
+/* O = softmax_rows(scale * Q K^T) V with bf16 Q (nq x d), K (nkv x d), V (nkv x d), O (nq x d),
+ * all row-major; S and P stay in TMEM / shared memory.  d must be 128 in this build.  The
+ * nearest reference analogue is the chained-GEMM fusion with a per-tile temporary
+ * (test/test-cpu-mm.cpp:266-408). */
+int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
+                         const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
+                         int64_t nkv, int64_t d, float scale, void *stream);
+
+/* ---- host-buffer forms (operands and results in host memory) -------------------------- */
+
+int gb200_gemm_f32_host(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
+                        float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate);
+int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                         void *C, int64_t ldc, int64_t M, int64_t N, int64_t K);
+int gb200_softmax_rows_f32_host(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
+                                int64_t ld_out, int64_t rows, int64_t cols);
+int gb200_blur3x3_f32_host(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
+                           int64_t in_cols, float *out, int64_t out_ld);
+int gb200_attention_bf16_host(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K,
+                              int64_t ldk, const void *V, int64_t ldv, void *O, int64_t ldo,
+                              int64_t nq, int64_t nkv, int64_t d, float scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GERN_B200_H */

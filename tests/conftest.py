@@ -1,0 +1,37 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU")
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import pyoracle
+    return pyoracle.Oracle()
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return np.load(os.path.join(ROOT, "tests", "golden", "golden.npz"))
+
+
+@pytest.fixture(scope="session")
+def ctx():
+    """The library context on cuda:0.  The shared library must already be built in-tree; there is
+    no fallback."""
+    import torch
+    assert torch.cuda.is_available(), "gpu-marked test run without a GPU"
+    from gern_b200 import api
+    c = api.Context(0)
+    yield c
+    c.sync()
+    c.close()

@@ -1,0 +1,99 @@
+"""GEMM -> row softmax -> GEMM chain: CUDA path against the fp32 CPU oracle on the same
+bf16-rounded inputs.  Tolerance: relative Frobenius error <= 1e-2 (north-star bar)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def frob(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def bits(t):
+    return np.ascontiguousarray(t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+
+
+def make(nq, nkv, seed, std=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = (torch.randn((nq, 128), generator=g, device="cuda") * std).to(torch.bfloat16)
+    k = (torch.randn((nkv, 128), generator=g, device="cuda") * std).to(torch.bfloat16)
+    v = (torch.randn((nkv, 128), generator=g, device="cuda") * std).to(torch.bfloat16)
+    return q, k, v
+
+
+@pytest.mark.parametrize("nq,nkv", [(128, 128), (128, 256), (256, 1024), (100, 200), (1, 1), (130, 129), (384, 4096)])
+def test_against_oracle(ctx, oracle, nq, nkv):
+    q, k, v = make(nq, nkv, nq + nkv)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / np.sqrt(128.0)
+    ctx.attention_bf16(q, k, v, o, scale)
+    ctx.sync()
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), scale)
+    oracle.set_threads(1)
+    assert frob(o.float().cpu().numpy(), want) <= 1e-2
+
+
+def test_peaked_rows_exercise_the_rescale(ctx, oracle):
+    """Large logits whose maximum keeps growing along kv force the running-max correction."""
+    nq, nkv = 128, 1024
+    q, k, v = make(nq, nkv, 5, std=1.0)
+    ramp = torch.linspace(0.2, 3.0, nkv, device="cuda").unsqueeze(1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    ctx.attention_bf16(q, k, v, o, 1.0)
+    ctx.sync()
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), 1.0)
+    assert frob(o.float().cpu().numpy(), want) <= 1e-2
+
+
+def test_uniform_scores_average_v(ctx):
+    nq, nkv = 128, 512
+    q = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    _, k, v = make(nq, nkv, 3)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    ctx.attention_bf16(q, k, v, o, 1.0)
+    ctx.sync()
+    want = v.float().mean(dim=0, keepdim=True).expand(nq, 128)
+    assert float((o.float() - want).abs().max()) < 2e-2
+
+
+def test_unsupported_head_dim_is_reported(ctx):
+    from gern_b200 import api
+    x = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(api.GernB200Error) as e:
+        ctx.attention_bf16(x, x, x, x, 1.0)
+    assert e.value.code == -3
+
+
+def test_full_size_sampled(ctx, oracle):
+    nq, nkv = 32768, 4096
+    q, k, v = make(nq, nkv, 0)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / np.sqrt(128.0)
+    ctx.attention_bf16(q, k, v, o, scale)
+    ctx.sync()
+    rows = slice(16000, 16128)
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.attention_bf16(bits(q[rows]), bits(k), bits(v), scale)
+    oracle.set_threads(1)
+    assert frob(o[rows].float().cpu().numpy(), want) <= 1e-2
+    # rows are independent: any row block alone gives the same bits
+    o2 = torch.zeros((256, 128), dtype=torch.bfloat16, device="cuda")
+    ctx.attention_bf16(q[1024:1280].contiguous(), k, v, o2, scale)
+    ctx.sync()
+    assert torch.equal(o2, o[1024:1280])
+
+
+def test_host_entry_point(ctx, oracle):
+    from oracle import pyoracle
+    rng = np.random.default_rng(1)
+    q = pyoracle.to_bf16_bits(rng.standard_normal((200, 128)).astype(np.float32))
+    k = pyoracle.to_bf16_bits(rng.standard_normal((300, 128)).astype(np.float32))
+    v = pyoracle.to_bf16_bits(rng.standard_normal((300, 128)).astype(np.float32))
+    o = np.zeros((200, 128), np.uint16)
+    scale = 1.0 / np.sqrt(128.0)
+    ctx.attention_bf16_host(q, k, v, o, scale)
+    assert frob(pyoracle.bf16_bits_to_f32(o), oracle.attention_bf16(q, k, v, scale)) <= 1e-2

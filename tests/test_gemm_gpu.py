@@ -1,0 +1,150 @@
+"""Matrix multiply: CUDA paths against the CPU oracle.
+fp32: |delta| <= 1e-3 absolute as in the reference's app self-checks (gernels/mm/float-error.h:2-4)
+and relative Frobenius error <= 1e-5 against the tiled Gern CPU path (fma vs mul+add rounding and
+K-tile reassociation are the only differences).
+bf16: relative Frobenius error <= 1e-2 against the fp32 oracle on the same bf16-rounded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import pyoracle
+
+pytestmark = pytest.mark.gpu
+
+
+def frob(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def test_f32_golden_10x10(ctx, golden):
+    a = torch.arange(100, dtype=torch.float32, device="cuda").reshape(10, 10)
+    c = torch.zeros((10, 10), device="cuda")
+    ctx.gemm_f32(a, a, c)
+    ctx.sync()
+    assert np.array_equal(c.cpu().numpy(), golden["mm10_c"])  # integers: exact
+
+
+def test_f32_512_against_gern_cpu_path(ctx, oracle, golden):
+    a_np = pyoracle.mt19937_uniform(512 * 512, -1.0, 1.0).reshape(512, 512)
+    a = torch.from_numpy(a_np).cuda()
+    c = torch.zeros((512, 512), device="cuda")
+    ctx.gemm_f32(a, a, c)
+    ctx.sync()
+    got = c.cpu().numpy()
+    assert np.abs(got[::8, ::8] - golden["mm512_sub"]).max() < 1e-3
+    assert frob(got[::8, ::8], golden["mm512_sub"]) < 1e-5
+    assert abs(got.astype(np.float64).sum() - float(golden["mm512_sum"])) < 1e-2 * 512
+
+
+@pytest.mark.parametrize("mnk", [(1, 1, 1), (5, 7, 3), (33, 65, 17), (64, 64, 64), (100, 130, 250), (257, 129, 513),
+                                 (2048, 2304, 96)])
+def test_f32_shapes(ctx, oracle, mnk):
+    m, n, k = mnk
+    rng = np.random.default_rng(m * 1000 + n)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.matmul_tiled(a, b, 64, 64, 64, c0.copy())
+    oracle.set_threads(1)
+    ag, bg, cg = (torch.from_numpy(t).cuda() for t in (a, b, c0))
+    ctx.gemm_f32(ag, bg, cg, accumulate=True)
+    ctx.sync()
+    got = cg.cpu().numpy()
+    assert np.abs(got - want).max() < 1e-3
+    assert frob(got, want) < 1e-5
+    ctx.gemm_f32(ag, bg, cg, accumulate=False)
+    ctx.sync()
+    assert frob(cg.cpu().numpy(), want - c0) < 1e-5
+
+
+def test_f32_k_zero_and_empty(ctx):
+    c = torch.full((4, 4), 3.0, device="cuda")
+    a = torch.zeros((4, 0), device="cuda")
+    b = torch.zeros((0, 4), device="cuda")
+    from gern_b200 import api
+    assert api.lib.gb200_gemm_f32(ctx.handle, None, 0, None, 4, c.data_ptr(), 4, 4, 4, 0, 1, None) == 0
+    ctx.sync()
+    assert bool((c == 3.0).all())
+    assert api.lib.gb200_gemm_f32(ctx.handle, None, 0, None, 4, c.data_ptr(), 4, 0, 4, 4, 0, None) == 0
+
+
+def run_bf16(ctx, m, n, k, seed, std=0.02, pad=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = (torch.randn((m, k + pad), generator=g, device="cuda") * std).to(torch.bfloat16)
+    b = (torch.randn((n, k + pad), generator=g, device="cuda") * std).to(torch.bfloat16)
+    c = torch.zeros((m, n + pad), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm_bf16(a[:, :k], b[:, :k], c[:, :n])
+    ctx.sync()
+    return a[:, :k], b[:, :k], c[:, :n]
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (100, 200, 72), (130, 258, 136),
+                                 (1, 8, 8), (384, 768, 1024), (1024, 1024, 1024)])
+def test_bf16_against_oracle(ctx, oracle, mnk):
+    m, n, k = mnk
+    a, b, c = run_bf16(ctx, m, n, k, seed=m + n + k)
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.gemm_bf16(np.ascontiguousarray(bits(a.contiguous())), np.ascontiguousarray(bits(b.contiguous())))
+    oracle.set_threads(1)
+    got = c.float().cpu().numpy()
+    assert frob(got, want) <= 1e-2
+    # tighter: the only error beyond fp32 accumulation order is the final bf16 rounding (2^-9)
+    assert frob(got, want) <= 3e-3
+
+
+def test_bf16_unaligned_falls_to_simple_kernel(ctx, oracle):
+    a, b, c = run_bf16(ctx, 70, 90, 50, seed=1, pad=3)   # pitch not a multiple of 8 elements
+    want = oracle.gemm_bf16(np.ascontiguousarray(bits(a.contiguous())), np.ascontiguousarray(bits(b.contiguous())))
+    assert frob(c.float().cpu().numpy(), want) <= 3e-3
+
+
+def test_bf16_structured_exact(ctx):
+    """Identity and small-integer operands are exact in bf16, so the result must be exact: checks
+    operand layout (row-major A, column-major B) and tile addressing without any tolerance."""
+    m = n = k = 512
+    a = torch.randint(-4, 5, (m, k), device="cuda").to(torch.bfloat16)
+    eye = torch.eye(k, device="cuda", dtype=torch.bfloat16)
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm_bf16(a, eye, c)
+    ctx.sync()
+    assert torch.equal(c, a)
+    b = torch.randint(-4, 5, (n, k), device="cuda").to(torch.bfloat16)
+    ctx.gemm_bf16(a[:, :64].contiguous(), b[:, :64].contiguous(), c)
+    ctx.sync()
+    want = a[:, :64].float() @ b[:, :64].float().T
+    assert torch.equal(c.float(), want)
+
+
+def test_bf16_full_size_sampled(ctx, oracle):
+    """8192^3 (the benchmark size): sampled rows against the oracle, plus linearity A(2B) = 2(AB)."""
+    n = 8192
+    a, b, c = run_bf16(ctx, n, n, n, seed=0)
+    rows = [0, 1, 127, 128, 4095, 8191]
+    a_s = np.ascontiguousarray(bits(a[rows].contiguous()))
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.gemm_bf16(a_s, np.ascontiguousarray(bits(b.contiguous())))
+    oracle.set_threads(1)
+    assert frob(c[rows].float().cpu().numpy(), want) <= 1e-2
+    c2 = torch.empty_like(c)
+    ctx.gemm_bf16(a, (b * 2).contiguous(), c2)
+    ctx.sync()
+    assert torch.equal(c2.float(), c.float() * 2)
+
+
+def test_host_entry_points(ctx, oracle):
+    rng = np.random.default_rng(2)
+    a = rng.uniform(-1, 1, (200, 300)).astype(np.float32)
+    b = rng.uniform(-1, 1, (300, 150)).astype(np.float32)
+    c = np.zeros((200, 150), np.float32)
+    ctx.gemm_f32_host(a, b, c)
+    assert frob(c, oracle.matrix_multiply(a, b)) < 1e-5
+    ab = pyoracle.to_bf16_bits((rng.standard_normal((256, 320)) * 0.02).astype(np.float32))
+    bb = pyoracle.to_bf16_bits((rng.standard_normal((512, 320)) * 0.02).astype(np.float32))
+    cb = np.zeros((256, 512), np.uint16)
+    ctx.gemm_bf16_host(ab, bb, cb)
+    assert frob(pyoracle.bf16_bits_to_f32(cb), oracle.gemm_bf16(ab, bb)) <= 3e-3

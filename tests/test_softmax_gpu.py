@@ -1,0 +1,90 @@
+"""Row softmax: CUDA path against the CPU oracle.  Tolerance: max elementwise relative error
+<= 1e-5 (north-star bar for fp32 softmax), with an absolute floor of 1e-30 for underflowed tails."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+REL_TOL = 1e-5
+
+
+def rel_err(got, want):
+    return float((np.abs(got.astype(np.float64) - want) / np.maximum(np.abs(want), 1e-30)).max())
+
+
+def run_softmax(ctx, x_np, pad=0):
+    rows, cols = x_np.shape
+    xin = torch.zeros((rows, cols + pad), dtype=torch.float32, device="cuda")
+    xin[:, :cols] = torch.from_numpy(x_np).cuda()
+    out = torch.full((rows, cols + pad), -7.0, dtype=torch.float32, device="cuda")
+    ctx.softmax_rows(xin[:, :cols], out[:, :cols])
+    ctx.sync()
+    o = out.cpu().numpy()
+    if pad:
+        assert (o[:, cols:] == -7.0).all()
+    return np.ascontiguousarray(o[:, :cols])
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 4), (5, 33), (7, 128), (64, 132), (33, 256), (9, 500), (16, 512),
+                                   (10, 1000), (8, 1024), (5, 2048), (12, 4096), (300, 4096), (3, 4100),
+                                   (2, 10000), (1000, 36)])
+def test_matches_oracle(ctx, oracle, shape):
+    x = (np.random.default_rng(shape[0] * 31 + shape[1]).standard_normal(shape) * 3).astype(np.float32)
+    got = run_softmax(ctx, x)
+    assert rel_err(got, oracle.softmax_rows(x)) <= REL_TOL
+    assert rel_err(got, oracle.softmax_rows_f64(x)) <= REL_TOL
+    assert np.allclose(got.sum(axis=1), 1.0, atol=2e-5)
+
+
+def test_golden_fixture(ctx, golden):
+    x = np.ascontiguousarray(golden["sm_in"])
+    assert rel_err(run_softmax(ctx, x), golden["sm_div"]) <= REL_TOL
+
+
+def test_padded_and_unaligned(ctx, oracle):
+    x = (np.random.default_rng(5).standard_normal((50, 257)) * 3).astype(np.float32)
+    assert rel_err(run_softmax(ctx, x, pad=3), oracle.softmax_rows(x)) <= REL_TOL
+    y = (np.random.default_rng(6).standard_normal((50, 256)) * 3).astype(np.float32)
+    assert rel_err(run_softmax(ctx, y, pad=4), oracle.softmax_rows(y)) <= REL_TOL
+
+
+def test_shift_invariance_and_extremes(ctx, oracle):
+    x = (np.random.default_rng(8).standard_normal((32, 4096)) * 3).astype(np.float32)
+    base = run_softmax(ctx, x)
+    shifted = run_softmax(ctx, x + np.float32(64.0))
+    assert rel_err(shifted, base) <= 1e-4  # inputs themselves are re-rounded by the shift
+    neg = -np.abs(x) - 50.0            # all-negative rows (breaks the reference's FLT_MIN max seed)
+    assert rel_err(run_softmax(ctx, neg), oracle.softmax_rows(neg)) <= REL_TOL
+    big = x * 30                        # peaked rows: most entries underflow
+    got = run_softmax(ctx, big)
+    assert np.isfinite(got).all() and np.allclose(got.sum(axis=1), 1.0, atol=2e-5)
+    const = np.full((4, 4096), 2.5, np.float32)
+    assert np.array_equal(run_softmax(ctx, const), np.full((4, 4096), 1.0 / 4096, np.float32))
+
+
+def test_empty(ctx):
+    for shape in ((0, 16), (16, 0)):
+        assert run_softmax(ctx, np.zeros(shape, np.float32)).size == 0
+
+
+def test_full_size_properties(ctx, oracle):
+    rows, cols = 65536, 4096
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((rows, cols), generator=g, device="cuda") * 3
+    out = torch.empty_like(x)
+    ctx.softmax_rows(x, out)
+    ctx.sync()
+    sums = out.sum(dim=1)
+    assert float((sums - 1).abs().max()) < 2e-5
+    assert bool((out >= 0).all())
+    assert torch.equal(out.argmax(dim=1), x.argmax(dim=1))
+    for r0 in (0, 30000, rows - 16):
+        xs = x[r0:r0 + 16].cpu().numpy()
+        assert rel_err(out[r0:r0 + 16].cpu().numpy(), oracle.softmax_rows(xs)) <= REL_TOL
+
+
+def test_host_entry_point(ctx, oracle):
+    x = (np.random.default_rng(4).standard_normal((5000, 1000)) * 3).astype(np.float32)
+    out = np.empty_like(x)
+    ctx.softmax_rows_host(x, out)
+    assert rel_err(out, oracle.softmax_rows(x)) <= REL_TOL
