@@ -35,8 +35,9 @@ struct BlurTmaCfg {
     static constexpr int NBOX = TW / 256;                 // a TMA box is at most 256 elements wide
     static constexpr int BOX_F = RS * 256;                // floats per main box
     static constexpr int PAD_F = RS * 4;                  // the 4 columns right of the strip
-    static constexpr int STAGE_F = NBOX * BOX_F + PAD_F;
-    static constexpr int STAGE_BYTES = STAGE_F * 4;       // multiple of 128
+    static constexpr int TX_BYTES = (NBOX * BOX_F + PAD_F) * 4;   // bytes TMA delivers per stage
+    static constexpr int STAGE_F = (NBOX * BOX_F + PAD_F + 31) / 32 * 32;  // 128-byte aligned stages
+    static constexpr int STAGE_BYTES = STAGE_F * 4;
     static constexpr int SMEM_BYTES = S * STAGE_BYTES + S * 8 + 128;
 };
 
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(TW / 4)
 blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map,
                    const __grid_constant__ CUtensorMap pad_map, float *__restrict__ out,
                    int64_t out_ld, int out_rows, int out_cols, int rows_per_band, int n_strips,
-                   int *status) {
+                   int out_vec, int *status) {
     using Cfg = BlurTmaCfg<TW, RS, S>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // The dynamic shared window is only guaranteed 16-byte aligned; TMA wants 128.
@@ -67,7 +68,7 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map,
     auto issue = [&](int chunk, int s) {
         float *dst = stage + s * Cfg::STAGE_F;
         const int y = r_begin + chunk * RS;
-        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+        mbar_expect_tx(&full[s], Cfg::TX_BYTES);
 #pragma unroll
         for (int b = 0; b < Cfg::NBOX; ++b)
             tma_load_2d(dst + b * Cfg::BOX_F, &in_map, x0 + b * 256, y, &full[s]);
@@ -103,7 +104,7 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map,
 
     const int c0 = x0 + tid * 4;                 // first output column of this thread
     const int ncol = min(4, out_cols - c0);      // <= 0: nothing to store
-    const bool vec_ok = (ncol == 4);
+    const bool vec_ok = (ncol == 4) && out_vec;  // 16-byte stores need an aligned output row
     float h0[4] = {0.f, 0.f, 0.f, 0.f}, h1[4] = {0.f, 0.f, 0.f, 0.f};
     bool alive = true;
 
@@ -264,7 +265,7 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
                                         Cfg::SMEM_BYTES));
     kern<<<(unsigned)(bands * n_strips), Cfg::NT, Cfg::SMEM_BYTES, stream>>>(
         tm, tm_pad, out, out_ld, (int)out_rows, (int)out_cols, (int)rows_per_band, n_strips,
-        ctx->d_status);
+        (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, ctx->d_status);
     return after_launch(ctx, "blur3x3_tma_kernel");
 }
 
@@ -281,12 +282,21 @@ static int check_blur_args(const float *in, int64_t in_ld, int64_t in_rows, int6
     return GB200_OK;
 }
 
-// variant: 0 = pick (TMA when aligned), 1 = direct kernel only.  Exposed for benchmarking.
+// variant: 0 = pick (TMA when aligned), 1 = direct kernel only, 2.. = other TMA tilings.
+// Exposed for benchmarking and for the parity tests of the non-default kernels.
 int blur_dispatch(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows, int64_t in_cols,
                   float *out, int64_t out_ld, cudaStream_t stream, int variant) {
     const bool tma_ok = variant != 1 && ctx->encode_tiled && aligned16(in) && in_ld % 4 == 0 &&
                         in_cols >= 64 && in_rows >= 16;
-    if (tma_ok) return launch_tma<256, 8, 4>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+    if (tma_ok) {
+        switch (variant) {
+            case 2: return launch_tma<512, 8, 3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+            case 3: return launch_tma<256, 4, 8>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+            case 4: return launch_tma<256, 16, 3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+            case 5: return launch_tma<512, 4, 6>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+            default: return launch_tma<256, 8, 4>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        }
+    }
     return launch_direct(ctx, in, in_ld, in_rows, nullptr, 0, in_cols, out, out_ld, 0, in_rows - 2,
                          stream);
 }

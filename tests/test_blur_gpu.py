@@ -35,6 +35,16 @@ def test_matches_oracle(ctx, oracle, shape, variant):
     assert np.array_equal(run_blur(ctx, x, variant), oracle.blur_xy(x))
 
 
+@pytest.mark.parametrize("shape", [(16, 66), (40, 262), (130, 1030), (600, 2054)])
+def test_aligned_output_rows_take_vector_stores(ctx, oracle, shape):
+    # cols - 2 is a multiple of 4: output rows are 16-byte aligned, so the 128-bit store path runs
+    x = np.random.default_rng(shape[1]).random(shape, dtype=np.float32)
+    want = oracle.blur_xy(x)
+    assert np.array_equal(run_blur(ctx, x, None, in_pad=2), want)
+    assert np.array_equal(run_blur(ctx, x, 1, in_pad=2), want)
+    assert np.array_equal(run_blur(ctx, x, None, in_pad=2, out_pad=4), want)
+
+
 def test_padded_leading_dimensions_and_unaligned(ctx, oracle):
     x = np.random.default_rng(1).random((200, 777), dtype=np.float32)
     want = oracle.blur_xy(x)
@@ -92,17 +102,24 @@ def test_full_size_properties(ctx, oracle):
     n = 8192
     g = torch.Generator(device="cuda").manual_seed(0)
     x = torch.rand((n, n), generator=g, device="cuda")
-    a = torch.empty((n - 2, n - 2), device="cuda")
-    b = torch.empty((n - 2, n - 2), device="cuda")
-    ctx.blur3x3(x, a)
-    ctx.blur3x3(x, b, variant=1)
+    # the benchmark's shape: 8188 x 8188 out of the 8192 x 8192 stored image (ld 8192 / 8188)
+    xin = x[: n - 2, : n - 2]
+    a = torch.empty((n - 4, n - 4), device="cuda")
+    b = torch.empty((n - 4, n - 4), device="cuda")
+    ctx.blur3x3(xin, a)
+    ctx.blur3x3(xin, b, variant=1)
     ctx.sync()
     assert torch.equal(a, b)
-    for r0 in (0, 4093, n - 2 - 6):
-        xs = x[r0:r0 + 8].cpu().numpy()
+    for r0 in (0, 4093, n - 4 - 6):
+        xs = np.ascontiguousarray(xin[r0:r0 + 8].cpu().numpy())
         assert np.array_equal(a[r0:r0 + 6].cpu().numpy(), oracle.blur_xy(xs))
+    # whole image, unaligned output rows (8190 wide)
+    c = torch.empty((n - 2, n - 2), device="cuda")
+    ctx.blur3x3(x, c)
+    ctx.sync()
+    assert torch.equal(c[: n - 4, : n - 4], a)
     x.fill_(0.75)
-    ctx.blur3x3(x, a)
+    ctx.blur3x3(xin, a)
     ctx.sync()
     assert bool((a == 0.75).all())
 
