@@ -556,6 +556,8 @@ def main():
     ap.add_argument("--impl", default="gern_b200", choices=["gern_b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--small", action="store_true",
+                    help="reduced sizes (still larger than L2) for profiler captures; not a bench number")
     ap.add_argument("--also", default="softmax,gemm_bf16,attention",
                     help="comma list of further workloads summarised under 'also' (N=1 only)")
     args = ap.parse_args()
@@ -584,6 +586,11 @@ def main():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.small:
+        SoftmaxWorkload.ROWS = 16384
+        GemmBf16Workload.N = 4096
+        AttentionWorkload.NQ = 8192
 
     def run_workload(name, steps, warmup, want_e2e, want_cpu):
         wl = WORKLOADS[name](ctx, rank, world, torch, dist)
@@ -663,7 +670,7 @@ def main():
     main_res = run_workload(args.workload, args.steps, args.warmup, not args.no_e2e, not args.no_cpu_baseline)
     also = {}
     if world == 1 and args.also:
-        for name in [s for s in args.also.split(",") if s and s != args.workload]:
+        for name in [s for s in args.also.split(",") if s in WORKLOADS and s != args.workload]:
             try:
                 r = run_workload(name, min(args.steps, 10), 3, False, False)
                 also[name] = {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
@@ -675,7 +682,8 @@ def main():
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": main_res["ms_per_step"], "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": main_res["dtype"], "data": "synthetic",
-                "config": main_res["config"], "roofline": main_res["roofline"],
+                "config": dict(main_res["config"], **({"small": True} if args.small else {})),
+                "roofline": main_res["roofline"],
                 "gpu_launches": main_res["gpu_launches"], "clocks": main_res["clocks"]}
         if "e2e" in main_res:
             line["e2e"] = main_res["e2e"]

@@ -32,6 +32,7 @@ SIGNATURES = {
     "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
     "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
     "gb200_softmax_rows_f32": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
+    "gb200_softmax_rows_f32_variant": [_vp, _i64, _vp, _i64, _i64, _i64, _vp, _int],
     "gb200_blur3x3_f32": [_vp, _i64, _i64, _i64, _vp, _i64, _vp],
     "gb200_blur3x3_f32_variant": [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _int],
     "gb200_blur3x3_f32_band": [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp],
@@ -133,8 +134,13 @@ class Context:
         _check(lib.gb200_gemm_bf16(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N,
                                    K, _stream(stream)), "gb200_gemm_bf16")
 
-    def softmax_rows(self, x, out, stream=None):
+    def softmax_rows(self, x, out, stream=None, variant=None):
         rows, cols = x.shape
+        if variant is not None:
+            _check(lib.gb200_softmax_rows_f32_variant(self.handle, _ptr(x), _ld(x), _ptr(out), _ld(out),
+                                                      rows, cols, _stream(stream), int(variant)),
+                   "gb200_softmax_rows_f32_variant")
+            return
         _check(lib.gb200_softmax_rows_f32(self.handle, _ptr(x), _ld(x), _ptr(out), _ld(out), rows, cols,
                                           _stream(stream)), "gb200_softmax_rows_f32")
 

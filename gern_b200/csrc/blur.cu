@@ -25,126 +25,212 @@ __device__ __forceinline__ float div3(float x) {
     return fmaf(r, rc, q);
 }
 
+// Packed fp32x2 arithmetic (sm_100 has two-wide FADD/FMUL/FFMA): the same IEEE round-to-nearest
+// operations as the scalar code above on two lanes at once, so results stay bit-identical
+// while the instruction count of the stencil halves.
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t div3_2(uint64_t x) {
+    const uint64_t rc = pk2(0x1.555556p-2f, 0x1.555556p-2f);
+    const uint64_t m3 = pk2(-3.0f, -3.0f);
+    const uint64_t q = mul2(x, rc);
+    const uint64_t r = fma2(m3, q, x);
+    return fma2(r, rc, q);
+}
+// Horizontal pass on 4 adjacent outputs: inputs a = in[c..c+3], b = in[c+4..c+5].
+// h[k] = ((in[c+k] + in[c+k+1]) + in[c+k+2]) / 3, returned as two packed pairs.
+__device__ __forceinline__ void hpass4(const float4 a, const float2 b, uint64_t &h01, uint64_t &h23) {
+    const uint64_t a01 = pk2(a.x, a.y), a12 = pk2(a.y, a.z), a23 = pk2(a.z, a.w);
+    const uint64_t a3b = pk2(a.w, b.x), b01 = pk2(b.x, b.y);
+    h01 = div3_2(add2(add2(a01, a12), a23));
+    h23 = div3_2(add2(add2(a23, a3b), b01));
+}
+// Vertical pass: ((t0 + t1) + t2) / 3 on a packed pair.
+__device__ __forceinline__ uint64_t vpass2(uint64_t t0, uint64_t t1, uint64_t t2) {
+    return div3_2(add2(add2(t0, t1), t2));
+}
+__device__ __forceinline__ void store4(float *dst, uint64_t o01, uint64_t o23, int ncol, bool vec) {
+    if (vec) {
+        *reinterpret_cast<ulonglong2 *>(dst) = make_ulonglong2(o01, o23);
+    } else {
+        float o[4];
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(o[0]), "=f"(o[1]) : "l"(o01));
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(o[2]), "=f"(o[3]) : "l"(o23));
+        for (int k = 0; k < ncol; ++k) dst[k] = o[k];
+    }
+}
+
 // ---------------------------------------------------------------------------------------
-// TMA kernel: strip width TW output columns, NT = TW/4 threads, ring of S stages of RS rows.
+// TMA-staged kernel: every warp owns a 128-column strip of a row band and runs its own ring of
+// S stages of RS rows x 132 columns (one TMA box: the strip plus the 4 columns to its right)
+// with private mbarriers, so no block-level barrier exists and warps drift freely.  The stencil
+// runs on fp32x2 pairs, the output pointer is carried instead of recomputed, and whole chunks
+// of interior lanes take a branch-free path.  Measured slower on B200 than the register-staged
+// kernel below (long-lived strips spread the DRAM accesses over the whole image), so it is an
+// alternative, not the default.
 // ---------------------------------------------------------------------------------------
-template <int TW, int RS, int S>
-struct BlurTmaCfg {
-    static_assert(TW % 256 == 0, "strip width is a whole number of 256-column TMA boxes");
-    static constexpr int NT = TW / 4;
-    static constexpr int NBOX = TW / 256;                 // a TMA box is at most 256 elements wide
-    static constexpr int BOX_F = RS * 256;                // floats per main box
-    static constexpr int PAD_F = RS * 4;                  // the 4 columns right of the strip
-    static constexpr int TX_BYTES = (NBOX * BOX_F + PAD_F) * 4;   // bytes TMA delivers per stage
-    static constexpr int STAGE_F = (NBOX * BOX_F + PAD_F + 31) / 32 * 32;  // 128-byte aligned stages
-    static constexpr int STAGE_BYTES = STAGE_F * 4;
-    static constexpr int SMEM_BYTES = S * STAGE_BYTES + S * 8 + 128;
+template <int RS, int S>
+struct BlurWarpCfg {
+    static constexpr int WARPS = 4;
+    static constexpr int ROW_F = 132;                                 // 528 bytes per staged row
+    static constexpr int TX_BYTES = RS * ROW_F * 4;
+    static constexpr int STAGE_F = (RS * ROW_F + 31) / 32 * 32;      // stages start 128-byte aligned
+    static constexpr int WARP_F = S * STAGE_F;
+    static constexpr int SMEM_BYTES = WARPS * WARP_F * 4 + WARPS * S * 8 + 128;
 };
 
-template <int TW, int RS, int S>
-__global__ void __launch_bounds__(TW / 4)
-blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map,
-                   const __grid_constant__ CUtensorMap pad_map, float *__restrict__ out,
-                   int64_t out_ld, int out_rows, int out_cols, int rows_per_band, int n_strips,
-                   int out_vec, int *status) {
-    using Cfg = BlurTmaCfg<TW, RS, S>;
+template <int RS, int S>
+__global__ void __launch_bounds__(128)
+blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict__ out,
+                         int64_t out_ld, int out_rows, int out_cols, int rows_per_band,
+                         int n_strips, int n_items, int out_vec, int *status) {
+    using Cfg = BlurWarpCfg<RS, S>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    // The dynamic shared window is only guaranteed 16-byte aligned; TMA wants 128.
     unsigned char *base = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~static_cast<uintptr_t>(127));
-    float *stage = reinterpret_cast<float *>(base);
-    uint64_t *full = reinterpret_cast<uint64_t *>(base + S * Cfg::STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float *stage = reinterpret_cast<float *>(base) + warp * Cfg::WARP_F;
+    uint64_t *full = reinterpret_cast<uint64_t *>(base + Cfg::WARPS * Cfg::WARP_F * 4) + warp * S;
 
-    const int tid = threadIdx.x;
-    const int strip = blockIdx.x % n_strips;
-    const int band = blockIdx.x / n_strips;
-    const int x0 = strip * TW;
-    const int r_begin = band * rows_per_band;                     // first output row
-    const int r_end = min(r_begin + rows_per_band, out_rows);     // one past last output row
-    if (r_begin >= r_end) return;                                 // uniform over the CTA
+    const int item = blockIdx.x * Cfg::WARPS + warp;
+    if (item >= n_items) return;
+    const int strip = item % n_strips;
+    const int band = item / n_strips;
+    const int x0 = strip * 128;
+    const int r_begin = band * rows_per_band;
+    const int r_end = min(r_begin + rows_per_band, out_rows);
+    if (r_begin >= r_end) return;
     const int in_rows_needed = r_end - r_begin + 2;
     const int n_chunks = (in_rows_needed + RS - 1) / RS;
 
-    auto issue = [&](int chunk, int s) {
-        float *dst = stage + s * Cfg::STAGE_F;
-        const int y = r_begin + chunk * RS;
-        mbar_expect_tx(&full[s], Cfg::TX_BYTES);
-#pragma unroll
-        for (int b = 0; b < Cfg::NBOX; ++b)
-            tma_load_2d(dst + b * Cfg::BOX_F, &in_map, x0 + b * 256, y, &full[s]);
-        tma_load_2d(dst + Cfg::NBOX * Cfg::BOX_F, &pad_map, x0 + TW, y, &full[s]);
-    };
-
-    if (tid == 0) {
+    if (lane == 0) {
         prefetch_tmap(&in_map);
-        prefetch_tmap(&pad_map);
         for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
         mbar_fence_init();
-    }
-    __syncthreads();
-    if (tid == 0) {
         const int pre = n_chunks < S ? n_chunks : S;
-        for (int c = 0; c < pre; ++c) issue(c, c);
+        for (int c = 0; c < pre; ++c) {
+            mbar_expect_tx(&full[c], Cfg::TX_BYTES);
+            tma_load_2d(stage + c * Cfg::STAGE_F, &in_map, x0, r_begin + c * RS, &full[c]);
+        }
     }
+    __syncwarp();
 
-    // Where this thread's 4 + 2 input columns sit inside a stage.
-    const int box = tid / 64, lane64 = tid % 64;
-    const int a_off = box * Cfg::BOX_F + lane64 * 4;      // row stride 256
-    int b_off, b_stride;
-    if (lane64 < 63) {
-        b_off = a_off + 4;
-        b_stride = 256;
-    } else if (box + 1 < Cfg::NBOX) {
-        b_off = (box + 1) * Cfg::BOX_F;
-        b_stride = 256;
-    } else {
-        b_off = Cfg::NBOX * Cfg::BOX_F;
-        b_stride = 4;
-    }
-
-    const int c0 = x0 + tid * 4;                 // first output column of this thread
-    const int ncol = min(4, out_cols - c0);      // <= 0: nothing to store
-    const bool vec_ok = (ncol == 4) && out_vec;  // 16-byte stores need an aligned output row
-    float h0[4] = {0.f, 0.f, 0.f, 0.f}, h1[4] = {0.f, 0.f, 0.f, 0.f};
+    const int c0 = x0 + lane * 4;
+    const int ncol = min(4, out_cols - c0);
+    const bool vec_ok = (ncol == 4) && out_vec;
+    float *dst = out + static_cast<int64_t>(r_begin) * out_ld + c0;   // next output row
+    uint64_t t0a = 0, t0b = 0, t1a = 0, t1b = 0;                      // two previous rows of t
     bool alive = true;
 
     for (int c = 0; c < n_chunks; ++c) {
         const int s = c % S;
         const uint32_t parity = (c / S) & 1;
-        if (alive && !mbar_wait(&full[s], parity, status, 101)) alive = false;
-        const float *st = stage + s * Cfg::STAGE_F;
+        if (alive && !mbar_wait(&full[s], parity, status, 103)) alive = false;
+        const float *st = stage + s * Cfg::STAGE_F + lane * 4;
         const int rows_here = min(RS, in_rows_needed - c * RS);
+        if (c > 0 && rows_here == RS && vec_ok) {
+            // interior chunk, interior lane: RS outputs, no predicates
 #pragma unroll
-        for (int r = 0; r < RS; ++r) {
-            if (r < rows_here) {
-                const float4 a = *reinterpret_cast<const float4 *>(st + a_off + r * 256);
-                const float2 b = *reinterpret_cast<const float2 *>(st + b_off + r * b_stride);
-                float h[4];
-                h[0] = div3(a.x + a.y + a.z);
-                h[1] = div3(a.y + a.z + a.w);
-                h[2] = div3(a.z + a.w + b.x);
-                h[3] = div3(a.w + b.x + b.y);
-                const int in_r = c * RS + r;     // row index inside this band's input window
-                if (in_r >= 2 && ncol > 0) {
-                    float o[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) o[k] = div3(h0[k] + h1[k] + h[k]);
-                    float *dst = out + static_cast<int64_t>(r_begin + in_r - 2) * out_ld + c0;
-                    if (vec_ok) {
-                        __stcs(reinterpret_cast<float4 *>(dst), make_float4(o[0], o[1], o[2], o[3]));
-                    } else {
-                        for (int k = 0; k < ncol; ++k) dst[k] = o[k];
-                    }
+            for (int r = 0; r < RS; ++r) {
+                const float4 a = *reinterpret_cast<const float4 *>(st + r * Cfg::ROW_F);
+                const float2 b = *reinterpret_cast<const float2 *>(st + r * Cfg::ROW_F + 4);
+                uint64_t ta, tb;
+                hpass4(a, b, ta, tb);
+                *reinterpret_cast<ulonglong2 *>(dst) =
+                    make_ulonglong2(vpass2(t0a, t1a, ta), vpass2(t0b, t1b, tb));
+                dst += out_ld;
+                t0a = t1a; t0b = t1b; t1a = ta; t1b = tb;
+            }
+        } else {
+            for (int r = 0; r < rows_here; ++r) {
+                const float4 a = *reinterpret_cast<const float4 *>(st + r * Cfg::ROW_F);
+                const float2 b = *reinterpret_cast<const float2 *>(st + r * Cfg::ROW_F + 4);
+                uint64_t ta, tb;
+                hpass4(a, b, ta, tb);
+                if (c * RS + r >= 2) {
+                    if (ncol > 0) store4(dst, vpass2(t0a, t1a, ta), vpass2(t0b, t1b, tb), ncol, vec_ok);
+                    dst += out_ld;
                 }
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    h0[k] = h1[k];
-                    h1[k] = h[k];
-                }
+                t0a = t1a; t0b = t1b; t1a = ta; t1b = tb;
             }
         }
-        __syncthreads();  // every thread is done with stage s
-        if (tid == 0 && c + S < n_chunks) issue(c + S, s);
+        __syncwarp();  // every lane is done with stage s
+        if (lane == 0 && c + S < n_chunks) {
+            mbar_expect_tx(&full[s], Cfg::TX_BYTES);
+            tma_load_2d(stage + s * Cfg::STAGE_F, &in_map, x0, r_begin + (c + S) * RS, &full[s]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Register-staged kernel (the default) for images whose rows are 16-byte aligned: a block
+// covers 512 columns x ROWS output rows; a thread loads its 6 x (ROWS+2) input patch with
+// 128-bit + 64-bit loads, keeps the horizontal pass in registers and runs the stencil on fp32x2
+// pairs.  Blocks are short-lived and scheduled row-major in many waves, so the set of rows in
+// flight is a compact window that moves down the image: the 2-row overlap between vertically
+// adjacent blocks is served by L2, and DRAM sees long sequential runs.  Same tile shape as the
+// reference's emitted kernel (per-thread register patch, apps/blur/blur.cu:19-45), minus its
+// redundant read of the output tile and with 4 columns per thread.
+// ---------------------------------------------------------------------------------------
+template <int ROWS>
+__global__ void __launch_bounds__(128)
+blur3x3_direct2_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
+                       float *__restrict__ out, int64_t out_ld, int out_rows, int out_vec) {
+    const int out_cols = in_cols - 2;
+    const int c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
+    if (c0 >= out_cols) return;
+    const int r_begin = blockIdx.y * ROWS;
+    const int n_out = min(ROWS, out_rows - r_begin);
+    const int ncol = min(4, out_cols - c0);
+    const float *src = in + static_cast<int64_t>(r_begin) * in_ld + c0;
+    float *dst = out + static_cast<int64_t>(r_begin) * out_ld + c0;
+    if (n_out == ROWS && c0 + 6 <= in_cols && out_vec) {
+        float4 a[ROWS + 2];
+        float2 b[ROWS + 2];
+#pragma unroll
+        for (int r = 0; r < ROWS + 2; ++r) {
+            a[r] = __ldg(reinterpret_cast<const float4 *>(src + r * in_ld));
+            b[r] = __ldg(reinterpret_cast<const float2 *>(src + r * in_ld + 4));
+        }
+        uint64_t ta[ROWS + 2], tb[ROWS + 2];
+#pragma unroll
+        for (int r = 0; r < ROWS + 2; ++r) hpass4(a[r], b[r], ta[r], tb[r]);
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            *reinterpret_cast<ulonglong2 *>(dst + r * out_ld) = make_ulonglong2(
+                vpass2(ta[r], ta[r + 1], ta[r + 2]), vpass2(tb[r], tb[r + 1], tb[r + 2]));
+    } else {
+        // ragged bottom or right edge, or output rows that are not 16-byte aligned
+        uint64_t t0a = 0, t0b = 0, t1a = 0, t1b = 0;
+        for (int r = 0; r < n_out + 2; ++r) {
+            float v[6];
+#pragma unroll
+            for (int k = 0; k < 6; ++k) v[k] = (c0 + k < in_cols) ? src[r * in_ld + k] : 0.0f;
+            uint64_t ta, tb;
+            hpass4(make_float4(v[0], v[1], v[2], v[3]), make_float2(v[4], v[5]), ta, tb);
+            if (r >= 2)
+                store4(dst + (r - 2) * out_ld, vpass2(t0a, t1a, ta), vpass2(t0b, t1b, tb), ncol,
+                       ncol == 4 && out_vec);
+            t0a = t1a; t0b = t1b; t1a = ta; t1b = tb;
+        }
     }
 }
 
@@ -154,7 +240,7 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map,
 // One thread owns VEC adjacent output columns and walks down `rows_per_thread` output rows
 // with the two previous horizontal sums in registers.
 // ---------------------------------------------------------------------------------------
-template <int VEC>
+template <int VEC, bool STCS = false>
 __global__ void __launch_bounds__(128)
 blur3x3_direct_kernel(const float *__restrict__ in, int64_t in_ld, int in_rows_local,
                       const float *__restrict__ halo, int64_t halo_ld, int in_cols,
@@ -199,7 +285,10 @@ blur3x3_direct_kernel(const float *__restrict__ in, int64_t in_ld, int in_rows_l
         for (int k = 0; k < VEC; ++k) o[k] = div3(h0[k] + h1[k] + h2[k]);
         float *dst = out + static_cast<int64_t>(r) * out_ld + c0;
         if (VEC == 4 && ncol == 4) {
-            *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[VEC - 1]);
+            if (STCS)
+                __stcs(reinterpret_cast<float4 *>(dst), make_float4(o[0], o[1], o[2], o[VEC - 1]));
+            else
+                *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[VEC - 1]);
         } else {
             for (int k = 0; k < ncol; ++k) dst[k] = o[k];
         }
@@ -216,17 +305,21 @@ static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 
 // Launches the direct kernel over output rows [row_begin, row_end).
 static int launch_direct(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows_local,
                          const float *halo, int64_t halo_ld, int64_t in_cols, float *out,
-                         int64_t out_ld, int64_t row_begin, int64_t row_end, cudaStream_t stream) {
+                         int64_t out_ld, int64_t row_begin, int64_t row_end, cudaStream_t stream,
+                         int rows_per_thread = 32, bool stcs = false) {
     if (row_end <= row_begin) return GB200_OK;
     const int64_t out_cols = in_cols - 2;
     const bool vec = aligned16(in) && aligned16(out) && in_ld % 4 == 0 && out_ld % 4 == 0 &&
                      (halo == nullptr || (aligned16(halo) && halo_ld % 4 == 0));
-    const int rows_per_thread = 32;
     const int vecw = vec ? 4 : 1;
     dim3 block(128);
     dim3 grid((unsigned)((out_cols + vecw * 128 - 1) / (vecw * 128)),
               (unsigned)((row_end - row_begin + rows_per_thread - 1) / rows_per_thread));
-    if (vec)
+    if (vec && stcs)
+        blur3x3_direct_kernel<4, true><<<grid, block, 0, stream>>>(
+            in, in_ld, (int)in_rows_local, halo, halo_ld, (int)in_cols, out, out_ld,
+            (int)row_begin, (int)row_end, rows_per_thread);
+    else if (vec)
         blur3x3_direct_kernel<4><<<grid, block, 0, stream>>>(
             in, in_ld, (int)in_rows_local, halo, halo_ld, (int)in_cols, out, out_ld,
             (int)row_begin, (int)row_end, rows_per_thread);
@@ -237,36 +330,46 @@ static int launch_direct(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t
     return after_launch(ctx, "blur3x3_direct_kernel");
 }
 
-template <int TW, int RS, int S>
+template <int RS, int S>
 static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
-                      int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream) {
-    using Cfg = BlurTmaCfg<TW, RS, S>;
+                            int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream,
+                            int waves = 1) {
+    using Cfg = BlurWarpCfg<RS, S>;
     const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
-    CUtensorMap tm, tm_pad;
+    CUtensorMap tm;
     int rc = get_tmap_2d(ctx, in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)in_cols,
-                         (uint64_t)in_rows, (uint64_t)in_ld * 4, 256, RS,
+                         (uint64_t)in_rows, (uint64_t)in_ld * 4, Cfg::ROW_F, RS,
                          CU_TENSOR_MAP_SWIZZLE_NONE, &tm);
     if (rc) return rc;
-    rc = get_tmap_2d(ctx, in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)in_cols,
-                     (uint64_t)in_rows, (uint64_t)in_ld * 4, 4, RS, CU_TENSOR_MAP_SWIZZLE_NONE,
-                     &tm_pad);
-    if (rc) return rc;
-    const int n_strips = (int)((out_cols + TW - 1) / TW);
-    // One wave of CTAs: as many row bands as fit the resident-CTA budget of the device.
-    const int ctas_per_sm = (int)((ctx->smem_optin + 1024) / (Cfg::SMEM_BYTES + 1024));
-    int64_t target = (int64_t)ctx->sm_count * (ctas_per_sm < 1 ? 1 : ctas_per_sm);
+    const int n_strips = (int)((out_cols + 127) / 128);
+    int ctas_per_sm = (int)((ctx->smem_optin + 1024) / (Cfg::SMEM_BYTES + 1024));
+    if (ctas_per_sm > 16) ctas_per_sm = 16;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    const int64_t target = (int64_t)ctx->sm_count * ctas_per_sm * Cfg::WARPS * waves;
     int64_t bands = target / n_strips;
     if (bands < 1) bands = 1;
     int64_t rows_per_band = (out_rows + bands - 1) / bands;
     if (rows_per_band < 8) rows_per_band = 8;
     bands = (out_rows + rows_per_band - 1) / rows_per_band;
-    auto kern = blur3x3_tma_kernel<TW, RS, S>;
+    const int64_t n_items = bands * n_strips;
+    auto kern = blur3x3_tma_kernel<RS, S>;
     GB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         Cfg::SMEM_BYTES));
-    kern<<<(unsigned)(bands * n_strips), Cfg::NT, Cfg::SMEM_BYTES, stream>>>(
-        tm, tm_pad, out, out_ld, (int)out_rows, (int)out_cols, (int)rows_per_band, n_strips,
+    kern<<<(unsigned)((n_items + Cfg::WARPS - 1) / Cfg::WARPS), 128, Cfg::SMEM_BYTES, stream>>>(
+        tm, out, out_ld, (int)out_rows, (int)out_cols, (int)rows_per_band, n_strips, (int)n_items,
         (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, ctx->d_status);
     return after_launch(ctx, "blur3x3_tma_kernel");
+}
+
+template <int ROWS>
+static int launch_direct2(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
+                          int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream) {
+    const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
+    dim3 grid((unsigned)((out_cols + 511) / 512), (unsigned)((out_rows + ROWS - 1) / ROWS));
+    blur3x3_direct2_kernel<ROWS><<<grid, 128, 0, stream>>>(
+        in, in_ld, (int)in_cols, out, out_ld, (int)out_rows,
+        (aligned16(out) && out_ld % 4 == 0) ? 1 : 0);
+    return after_launch(ctx, "blur3x3_direct2_kernel");
 }
 
 static int check_blur_args(const float *in, int64_t in_ld, int64_t in_rows, int64_t in_cols,
@@ -282,23 +385,28 @@ static int check_blur_args(const float *in, int64_t in_ld, int64_t in_rows, int6
     return GB200_OK;
 }
 
-// variant: 0 = pick (TMA when aligned), 1 = direct kernel only, 2.. = other TMA tilings.
-// Exposed for benchmarking and for the parity tests of the non-default kernels.
+// variant 0 picks: the register-staged kernel for 16-byte aligned input rows, else the generic
+// kernel.  Other variants exist for the parity tests and for benchmarking:
+//   1 = generic direct kernel,  2 = TMA-staged kernel (one wave),  3 = TMA-staged, 4 waves,
+//   40 + k = register-staged kernel with 2, 3, 4, 6, 8 output rows per block (k = 0..4).
 int blur_dispatch(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows, int64_t in_cols,
                   float *out, int64_t out_ld, cudaStream_t stream, int variant) {
-    const bool tma_ok = variant != 1 && ctx->encode_tiled && aligned16(in) && in_ld % 4 == 0 &&
-                        in_cols >= 64 && in_rows >= 16;
-    if (tma_ok) {
-        switch (variant) {
-            case 2: return launch_tma<512, 8, 3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-            case 3: return launch_tma<256, 4, 8>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-            case 4: return launch_tma<256, 16, 3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-            case 5: return launch_tma<512, 4, 6>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-            default: return launch_tma<256, 8, 4>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-        }
+    const bool in_aligned = aligned16(in) && in_ld % 4 == 0;
+    const bool tma_ok = ctx->encode_tiled && in_aligned && in_cols >= 64 && in_rows >= 16;
+    if (variant == 1 || !in_aligned)
+        return launch_direct(ctx, in, in_ld, in_rows, nullptr, 0, in_cols, out, out_ld, 0,
+                             in_rows - 2, stream);
+    if (variant == 2 && tma_ok)
+        return launch_tma<8, 2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream, 1);
+    if (variant == 3 && tma_ok)
+        return launch_tma<8, 2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream, 4);
+    switch (variant) {
+        case 40: return launch_direct2<2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 41: return launch_direct2<3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 43: return launch_direct2<6>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 44: return launch_direct2<8>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        default: return launch_direct2<4>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
     }
-    return launch_direct(ctx, in, in_ld, in_rows, nullptr, 0, in_cols, out, out_ld, 0, in_rows - 2,
-                         stream);
 }
 
 }  // namespace gb200

@@ -6,7 +6,8 @@
 // write of the matrix.  The reference's leaves reduce a row across `stride` threads through
 // shared memory with two block barriers per reduction (impl.h:80-188); here one warp owns one
 // row, keeps it in registers as 128-bit vectors, and reduces with five xor-shuffles, so no
-// barrier or shared memory is involved.
+// barrier or shared memory is involved.  Rows longer than 1024 columns switch to a CTA per row
+// (softmax_cta_kernel) so that a thread holds at most 8 vectors and many warps stay resident.
 //
 // Numerics: expf (not __expf), true division, fp32 throughout.  The reference's pieces as
 // written are not a usable definition (its CPU subtract_vec computes max - x,
@@ -78,6 +79,68 @@ softmax_warp_kernel(const float *__restrict__ in, int64_t ld_in, float *__restri
     }
 }
 
+// CTA-per-row kernel for long rows: THREADS threads keep NV float4 each (cols <= 4*NV*THREADS),
+// so a thread needs few registers and many warps are resident to cover HBM latency.  Row max
+// and row sum go warp-shuffle -> shared memory -> every thread re-reduces the per-warp values
+// (one block barrier per reduction; the scratch is double-buffered by row parity so no third
+// barrier is needed).  Rows are dealt round-robin over a persistent grid.
+template <int NV, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+softmax_cta_kernel(const float *__restrict__ in, int64_t ld_in, float *__restrict__ out,
+                   int64_t ld_out, int64_t rows, int cols) {
+    constexpr int NW = THREADS / 32;
+    __shared__ float red_max[2][NW];
+    __shared__ float red_sum[2][NW];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int nvec = cols >> 2;
+    int parity = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+        const float4 *src = reinterpret_cast<const float4 *>(in + row * ld_in);
+        float4 v[NV];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = threadIdx.x + THREADS * i;
+            if (idx < nvec)
+                v[i] = __ldcs(src + idx);
+            else
+                v[i] = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+        }
+        float m = -FLT_MAX;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+        m = warp_max(m);
+        if (lane == 0) red_max[parity][wid] = m;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, red_max[parity][w]);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = threadIdx.x + THREADS * i;
+            if (idx < nvec) {
+                v[i].x = expf(v[i].x - m);
+                v[i].y = expf(v[i].y - m);
+                v[i].z = expf(v[i].z - m);
+                v[i].w = expf(v[i].w - m);
+                s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            }
+        }
+        s = warp_sum(s);
+        if (lane == 0) red_sum[parity][wid] = s;
+        __syncthreads();
+        s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) s += red_sum[parity][w];
+        float4 *dst = reinterpret_cast<float4 *>(out + row * ld_out);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int idx = threadIdx.x + THREADS * i;
+            if (idx < nvec)
+                __stcs(dst + idx, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
+        }
+    }
+}
+
 // Block-per-row kernel for everything else (any cols, any alignment): pass 1 finds the max,
 // pass 2 the sum, pass 3 writes; passes 2 and 3 re-read the row (from L2 for rows that fit).
 __global__ void __launch_bounds__(256)
@@ -131,11 +194,38 @@ static int launch_warp(gb200_ctx *ctx, const float *in, int64_t ld_in, float *ou
     return after_launch(ctx, "softmax_warp_kernel");
 }
 
+template <int NV, int THREADS>
+static int launch_cta(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out, int64_t ld_out,
+                      int64_t rows, int64_t cols, cudaStream_t stream) {
+    int per_sm = 2048 / THREADS;  // resident CTAs per SM by thread count
+    if (per_sm > 16) per_sm = 16;
+    int64_t blocks = (int64_t)ctx->sm_count * per_sm;
+    if (blocks > rows) blocks = rows;
+    softmax_cta_kernel<NV, THREADS><<<(unsigned)blocks, THREADS, 0, stream>>>(in, ld_in, out, ld_out,
+                                                                              rows, (int)cols);
+    return after_launch(ctx, "softmax_cta_kernel");
+}
+
 static int softmax_dispatch(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
-                            int64_t ld_out, int64_t rows, int64_t cols, cudaStream_t stream) {
+                            int64_t ld_out, int64_t rows, int64_t cols, cudaStream_t stream,
+                            int variant = 0) {
     const bool vec = (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_in % 4 == 0 &&
                      ld_out % 4 == 0 && cols % 4 == 0 && cols <= 4096;
+    const bool vec_ptr = (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(out) & 15) == 0 && ld_in % 4 == 0 &&
+                         ld_out % 4 == 0 && cols % 4 == 0;
+    // variant 0 picks; 1 forces the warp-per-row kernel (cols <= 4096), 2..4 force a CTA shape.
+    if (vec_ptr && variant == 2 && cols <= 4096)
+        return launch_cta<4, 256>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
+    if (vec_ptr && variant == 3 && cols <= 4096)
+        return launch_cta<2, 512>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
+    if (vec_ptr && variant != 1 && cols > 1024) {
+        if (cols <= 4096) return launch_cta<8, 128>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
+        if (cols <= 8192) return launch_cta<8, 256>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
+        if (cols <= 16384) return launch_cta<8, 512>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
+        if (cols <= 32768) return launch_cta<8, 1024>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
+    }
     if (vec) {
         if (cols <= 128) return launch_warp<1>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
         if (cols <= 256) return launch_warp<2>(ctx, in, ld_in, out, ld_out, rows, cols, stream);
@@ -175,6 +265,18 @@ int gb200_softmax_rows_f32(gb200_ctx *ctx, const float *in, int64_t ld_in, float
     if (rc) return rc < 0 ? rc : GB200_OK;
     return softmax_dispatch(ctx, in, ld_in, out, ld_out, rows, cols,
                             static_cast<cudaStream_t>(stream));
+}
+
+// Test / benchmark hook: same contract, kernel variant chosen by the caller.
+int gb200_softmax_rows_f32_variant(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
+                                   int64_t ld_out, int64_t rows, int64_t cols, void *stream,
+                                   int variant) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_softmax_args(in, ld_in, out, ld_out, rows, cols);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return softmax_dispatch(ctx, in, ld_in, out, ld_out, rows, cols,
+                            static_cast<cudaStream_t>(stream), variant);
 }
 
 int gb200_softmax_rows_f32_host(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,

@@ -23,13 +23,13 @@ def run_blur(ctx, x_np, variant=None, in_pad=0, out_pad=0):
 def test_golden_fixtures(ctx, golden):
     for tag in ("asc", "rnd"):
         x = np.ascontiguousarray(golden[f"blur_in_{tag}"])
-        for variant in (None, 1):
+        for variant in (None, 1, 2):
             assert np.array_equal(run_blur(ctx, x, variant), golden[f"blur_out_{tag}"])
 
 
 @pytest.mark.parametrize("shape", [(3, 3), (4, 7), (16, 64), (17, 65), (64, 260), (67, 131), (130, 259),
                                    (300, 1028), (257, 2050), (1024, 1024), (1026, 516)])
-@pytest.mark.parametrize("variant", [None, 1])
+@pytest.mark.parametrize("variant", [None, 1, 2, 3, 40, 44])
 def test_matches_oracle(ctx, oracle, shape, variant):
     x = np.random.default_rng(shape[0] * 7919 + shape[1]).random(shape, dtype=np.float32)
     assert np.array_equal(run_blur(ctx, x, variant), oracle.blur_xy(x))
@@ -40,8 +40,8 @@ def test_aligned_output_rows_take_vector_stores(ctx, oracle, shape):
     # cols - 2 is a multiple of 4: output rows are 16-byte aligned, so the 128-bit store path runs
     x = np.random.default_rng(shape[1]).random(shape, dtype=np.float32)
     want = oracle.blur_xy(x)
-    assert np.array_equal(run_blur(ctx, x, None, in_pad=2), want)
-    assert np.array_equal(run_blur(ctx, x, 1, in_pad=2), want)
+    for variant in (None, 1, 2, 3, 41, 43):
+        assert np.array_equal(run_blur(ctx, x, variant, in_pad=2), want)
     assert np.array_equal(run_blur(ctx, x, None, in_pad=2, out_pad=4), want)
 
 
@@ -107,9 +107,11 @@ def test_full_size_properties(ctx, oracle):
     a = torch.empty((n - 4, n - 4), device="cuda")
     b = torch.empty((n - 4, n - 4), device="cuda")
     ctx.blur3x3(xin, a)
-    ctx.blur3x3(xin, b, variant=1)
-    ctx.sync()
-    assert torch.equal(a, b)
+    for variant in (1, 2, 3):
+        b.zero_()
+        ctx.blur3x3(xin, b, variant=variant)
+        ctx.sync()
+        assert torch.equal(a, b), variant
     for r0 in (0, 4093, n - 4 - 6):
         xs = np.ascontiguousarray(xin[r0:r0 + 8].cpu().numpy())
         assert np.array_equal(a[r0:r0 + 6].cpu().numpy(), oracle.blur_xy(xs))
