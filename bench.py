@@ -161,7 +161,7 @@ class BlurWorkload(Workload):
     metric = "fused two-stage blur, algorithmic HBM bytes per second"
     unit = "GB/s"
     dtype = "f32"
-    kernel = "blur3x3_tma_kernel"
+    kernel = "blur3x3_reg_kernel"
     N = 8192
 
     def __init__(self, ctx, rank, world, torch, dist=None):
@@ -256,7 +256,7 @@ class SoftmaxWorkload(Workload):
     metric = "row softmax, algorithmic HBM bytes per second"
     unit = "GB/s"
     dtype = "f32"
-    kernel = "softmax_warp_kernel"
+    kernel = "softmax_cta_kernel"
     ROWS, COLS = 65536, 4096
 
     def __init__(self, ctx, rank, world, torch, dist=None):

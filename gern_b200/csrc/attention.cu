@@ -9,13 +9,19 @@
 // the A operand of the second multiply, and the softmax is computed online over 128-wide blocks
 // of K/V with a running row maximum and row sum.
 //
-// One CTA owns 128 rows of Q.  Warp 0 streams K and V blocks through 2-deep TMA rings; warp 1
-// issues tcgen05.mma for S_j = Q K_j^T (two TMEM buffers, so S_{j+1} is computed while block j is
-// in the softmax) and O += P_j V_j; warps 2-5 own one row of the tile per thread: they read S_j
-// from TMEM, update max/sum, write P_j to shared memory in the 128-byte-swizzled K-major layout
-// the MMA reads, rescale O in TMEM when the running maximum has grown by more than 2^8, and at
-// the end normalise and store O.  Every wait is bounded and reports through the status word.
+// One CTA owns two 128-row tiles of Q.  Warp 9 streams K and V blocks through one 3-slot TMA
+// ring (K_0 V_0 K_1 V_1 ...); warp 8 issues tcgen05.mma in the order P_t V_j, Q_t K_{j+1}^T for
+// tile t = 0, 1, so that while one tile's S is in the softmax the tensor pipe works on the other
+// tile; warps 0-3 (tile 0) and 4-7 (tile 1) own one row each: they read S_t from TMEM twice
+// (maximum, then exponentials; few registers stay live), update max/sum, write P_t to shared
+// memory in the 128-byte-swizzled K-major layout the MMA reads, rescale O_t in TMEM when the
+// running maximum has grown by more than 2^8, and at the end normalise and store O.  Half of
+// the exponentials run on the MUFU and half as a cubic on the FMA pipe, because at this shape
+// the 16-per-clock MUFU is as scarce as the tensor pipe.  Every wait is bounded and reports
+// through the status word.
 #include <float.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -23,20 +29,62 @@ namespace gb200 {
 
 namespace attn {
 constexpr int BM = 128, BN = 128, D = 128;
+constexpr int TILES = 2;                   // Q tiles (of BM rows) per CTA
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: any 128 x 128 bf16 tile (2 swizzle chunks)
 constexpr int CHUNK_BYTES = 128 * 128;     // 16 KiB: 128 rows x 64 bf16
-constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 192;
-// Q, P, K ring, V ring, then barriers
-constexpr int SMEM_BYTES = (2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + 256;
-constexpr uint32_t TMEM_COLS = 512;  // S0 [0,128) S1 [128,256) O [256,384)
+constexpr int KV_SLOTS = 3;                // one ring for K_0 V_0 K_1 V_1 ...
+constexpr int NUM_THREADS = 320;           // 8 softmax warps + MMA warp + TMA warp
+// Q (2 tiles), P (2 tiles), K/V ring, then barriers
+constexpr int SMEM_BYTES = (2 * TILES + KV_SLOTS) * TILE_BYTES + 1024 + 256;
+constexpr uint32_t TMEM_COLS = 512;        // S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512)
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 }  // namespace attn
+
+#ifdef GB200_ATTN_TRACE
+// Debug-only timeline (compiled out of the library): CTA 0 records clock64() at a few points.
+__device__ long long g_attn_trace[16 * 64];
+#define ATTN_TRACE(slot, j)                                                          \
+    do {                                                                             \
+        if (blockIdx.x == 0 && (j) < 64) g_attn_trace[(slot) * 64 + (j)] = clock64(); \
+    } while (0)
+#else
+#define ATTN_TRACE(slot, j) do { } while (0)
+#endif
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x for a pair on the FMA pipe (no MUFU): round x to the nearest integer n with the
+// 1.5*2^23 trick, evaluate a cubic for 2^f on f = x - n in [-0.5, 0.5], and add n into the
+// exponent field.  Relative error below 1e-3, under the bf16 rounding P receives next.  x is
+// clamped to >= -126 so that the exponent arithmetic cannot wrap.
+__device__ __forceinline__ uint64_t poly_exp2_pair(uint64_t x2) {
+    float x0, x1;
+    unpk2(x2, x0, x1);
+    x2 = pk2(fmaxf(x0, -126.0f), fmaxf(x1, -126.0f));
+    const uint64_t magic = pk2(12582912.0f, 12582912.0f);       // 1.5 * 2^23
+    const uint64_t neg_magic = pk2(-12582912.0f, -12582912.0f);
+    const uint64_t t = add2(x2, magic);
+    const uint64_t n = add2(t, neg_magic);
+    const uint64_t f = fma2(n, pk2(-1.0f, -1.0f), x2);
+    uint64_t p = fma2(f, pk2(0.0555041087f, 0.0555041087f), pk2(0.2402265069f, 0.2402265069f));
+    p = fma2(p, f, pk2(0.6931471806f, 0.6931471806f));
+    p = fma2(p, f, pk2(1.0f, 1.0f));
+    float p0, p1, t0, t1;
+    unpk2(p, p0, p1);
+    unpk2(t, t0, t1);
+    // p * 2^n: the low mantissa bits of t hold n; one integer multiply-add moves it into the exponent
+    p0 = __int_as_float(__float_as_int(t0) * 0x800000 + __float_as_int(p0));
+    p1 = __int_as_float(__float_as_int(t1) * 0x800000 + __float_as_int(p1));
+    return pk2(p0, p1);
+}
+__device__ __forceinline__ uint64_t mufu_exp2_pair(uint64_t x2) {
+    float x0, x1;
+    unpk2(x2, x0, x1);
+    return pk2(fast_exp2(x0), fast_exp2(x1));
 }
 
 __global__ void __launch_bounds__(attn::NUM_THREADS, 1)
@@ -48,24 +96,20 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    unsigned char *sQ = smem;
-    unsigned char *sP = smem + TILE_BYTES;
-    unsigned char *sK = smem + 2 * TILE_BYTES;
-    unsigned char *sV = smem + (2 + KV_STAGES) * TILE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (2 + 2 * KV_STAGES) * TILE_BYTES);
-    uint64_t *q_full = bars;           // [1]
-    uint64_t *k_full = bars + 1;       // [2]
-    uint64_t *k_empty = bars + 3;      // [2]
-    uint64_t *v_full = bars + 5;       // [2]
-    uint64_t *v_empty = bars + 7;      // [2]
-    uint64_t *s_full = bars + 9;       // [2]
-    uint64_t *s_free = bars + 11;      // [2]
-    uint64_t *p_ready = bars + 13;     // [1]
-    uint64_t *pv_done = bars + 14;     // [1]
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
+    unsigned char *sQ = smem;                               // [TILES] tiles
+    unsigned char *sP = smem + TILES * TILE_BYTES;          // [TILES] tiles
+    unsigned char *sKV = smem + 2 * TILES * TILE_BYTES;     // [KV_SLOTS] tiles
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (2 * TILES + KV_SLOTS) * TILE_BYTES);
+    uint64_t *q_full = bars;            // [1]
+    uint64_t *kv_full = bars + 1;       // [3]
+    uint64_t *kv_empty = bars + 4;      // [3]
+    uint64_t *s_full = bars + 7;        // [2] MMA -> softmax t: S_t holds block j
+    uint64_t *sp_ready = bars + 9;      // [2] softmax t -> MMA: P_t written, S_t consumed
+    uint64_t *o_full = bars + 11;       // [2] MMA -> softmax t: O_t final
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 13);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * BM;
+    const int q0 = blockIdx.x * (BM * TILES);
     const int n_blocks = (nkv + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
@@ -73,21 +117,18 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
         mbar_init(q_full, 1);
-        for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
-            mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
+        for (int s = 0; s < KV_SLOTS; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&s_full[b], 1);
-            mbar_init(&s_free[b], 4);
+        for (int t = 0; t < TILES; ++t) {
+            mbar_init(&s_full[t], 1);
+            mbar_init(&sp_ready[t], 4);
+            mbar_init(&o_full[t], 1);
         }
-        mbar_init(p_ready, 4);
-        mbar_init(pv_done, 1);
         mbar_fence_init();
     }
-    if (warp == 1) {
+    if (warp == 8) {
         tmem_alloc(tmem_slot, TMEM_COLS);
         tmem_relinquish();
     }
@@ -95,67 +136,51 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256;
 
-    if (warp == 0) {
+    if (warp == 9) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(q_full, TILE_BYTES);
-            tma_load_2d(sQ, &tmap_q, 0, q0, q_full);
-            tma_load_2d(sQ + CHUNK_BYTES, &tmap_q, 64, q0, q_full);
-            for (int j = 0; j < n_blocks; ++j) {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1;
-                if (!mbar_wait(&k_empty[st], ph ^ 1, status, 301)) break;
-                mbar_expect_tx(&k_full[st], TILE_BYTES);
-                tma_load_2d(sK + st * TILE_BYTES, &tmap_k, 0, j * BN, &k_full[st]);
-                tma_load_2d(sK + st * TILE_BYTES + CHUNK_BYTES, &tmap_k, 64, j * BN, &k_full[st]);
-                if (!mbar_wait(&v_empty[st], ph ^ 1, status, 302)) break;
-                mbar_expect_tx(&v_full[st], TILE_BYTES);
-                tma_load_2d(sV + st * TILE_BYTES, &tmap_v, 0, j * BN, &v_full[st]);
-                tma_load_2d(sV + st * TILE_BYTES + CHUNK_BYTES, &tmap_v, 64, j * BN, &v_full[st]);
+            mbar_expect_tx(q_full, TILES * TILE_BYTES);
+            for (int t = 0; t < TILES; ++t) {
+                tma_load_2d(sQ + t * TILE_BYTES, &tmap_q, 0, q0 + t * BM, q_full);
+                tma_load_2d(sQ + t * TILE_BYTES + CHUNK_BYTES, &tmap_q, 64, q0 + t * BM, q_full);
+            }
+            // ring order: K_0 V_0 K_1 V_1 ...
+            for (int u = 0; u < 2 * n_blocks; ++u) {
+                const int slot = u % KV_SLOTS;
+                const uint32_t ph = (u / KV_SLOTS) & 1;
+                if (!mbar_wait(&kv_empty[slot], ph ^ 1, status, 301)) break;
+                const CUtensorMap *tm = (u & 1) ? &tmap_v : &tmap_k;
+                unsigned char *dst = sKV + slot * TILE_BYTES;
+                mbar_expect_tx(&kv_full[slot], TILE_BYTES);
+                tma_load_2d(dst, tm, 0, (u >> 1) * BN, &kv_full[slot]);
+                tma_load_2d(dst + CHUNK_BYTES, tm, 64, (u >> 1) * BN, &kv_full[slot]);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 8) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, 0);  // A, B both K-major
             constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);   // B (= V) is MN-major
-            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
             bool ok = mbar_wait(q_full, 0, status, 303);
 
-            auto issue_qk = [&](int j) -> bool {
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1;
-                const int buf = j & 1;
-                if (!mbar_wait(&k_full[st], ph, status, 304)) return false;
-                // S[buf] was last read by the softmax of block j-2
-                if (!mbar_wait(&s_free[buf], ((j >> 1) & 1) ^ 1, status, 305)) return false;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+            auto wait_kv = [&](int u) -> bool {
+                return mbar_wait(&kv_full[u % KV_SLOTS], (u / KV_SLOTS) & 1, status, 304);
+            };
+            auto issue_qk = [&](int t, int j) {
+                const uint32_t q_addr = smem_u32(sQ + t * TILE_BYTES);
+                const uint32_t k_addr = smem_u32(sKV + ((2 * j) % KV_SLOTS) * TILE_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = (ks / 4) * CHUNK_BYTES + (ks % 4) * 32;
-                    umma_f16_ss(tmem_base + buf * BN, umma_desc_sw128(q_addr + off, 16, 1024),
+                    umma_f16_ss(tmem_base + t * BN, umma_desc_sw128(q_addr + off, 16, 1024),
                                 umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks != 0);
                 }
-                umma_commit(&k_empty[st]);
-                umma_commit(&s_full[buf]);
-                return true;
+                umma_commit(&s_full[t]);
             };
-
-            if (ok && n_blocks > 0) ok = issue_qk(0);
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                if (j + 1 < n_blocks) {
-                    ok = issue_qk(j + 1);
-                    if (!ok) break;
-                }
-                const int st = j % KV_STAGES;
-                const uint32_t ph = (j / KV_STAGES) & 1;
-                if (!mbar_wait(&v_full[st], ph, status, 306)) { ok = false; break; }
-                if (!mbar_wait(p_ready, j & 1, status, 307)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+            auto issue_pv = [&](int t, int j) {
+                const uint32_t p_addr = smem_u32(sP + t * TILE_BYTES);
+                const uint32_t v_addr = smem_u32(sKV + ((2 * j + 1) % KV_SLOTS) * TILE_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks) {
                     // A = P: K-major, 16 kv values = 32 bytes inside the swizzle row.
@@ -163,115 +188,175 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     // B = V: MN-major; 16 kv rows = 2048 bytes; the two 64-wide d chunks are
                     // CHUNK_BYTES apart (leading offset), 8-row groups 1024 bytes apart.
                     const uint32_t b_off = ks * 16 * 128;
-                    umma_f16_ss(tmem_o, umma_desc_sw128(p_addr + a_off, 16, 1024),
+                    umma_f16_ss(tmem_base + 256 + t * D, umma_desc_sw128(p_addr + a_off, 16, 1024),
                                 umma_desc_sw128(v_addr + b_off, CHUNK_BYTES, 1024), idesc_pv,
                                 (j | ks) != 0);
                 }
-                umma_commit(&v_empty[st]);
-                umma_commit(pv_done);
+            };
+
+            if (ok && n_blocks > 0) ok = wait_kv(0);
+            if (ok && n_blocks > 0) {
+                tc_fence_after();
+                issue_qk(0, 0);
+                issue_qk(1, 0);
+                umma_commit(&kv_empty[0]);
+            }
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                if (!wait_kv(2 * j + 1)) { ok = false; break; }
+                const bool more = j + 1 < n_blocks;
+                if (more && !wait_kv(2 * j + 2)) { ok = false; break; }
+                for (int t = 0; t < TILES; ++t) {
+                    if (!mbar_wait(&sp_ready[t], j & 1, status, 307)) { ok = false; break; }
+                    ATTN_TRACE(8 + 2 * t, j);
+                    tc_fence_after();
+                    issue_pv(t, j);
+                    if (more)
+                        issue_qk(t, j + 1);   // completes after PV(t, j): tensor pipe is in order
+                    else
+                        umma_commit(&o_full[t]);
+                    ATTN_TRACE(9 + 2 * t, j);
+                }
+                if (!ok) break;
+                umma_commit(&kv_empty[(2 * j + 1) % KV_SLOTS]);
+                if (more) umma_commit(&kv_empty[(2 * j + 2) % KV_SLOTS]);
             }
         }
     } else {
-        // ---------------- softmax / correction / epilogue: one row per thread ----------------
+        // ---------------- softmax / correction / epilogue ----------------
+        // warps 0-3 own Q tile 0, warps 4-7 own Q tile 1; one row per thread.
+        const int t = warp >> 2;
         const int lane_group = warp & 3;
         const int row_in_tile = lane_group * 32 + lane;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
-        const uint32_t t_o = t_row + 256;
+        const uint32_t t_s = t_row + t * BN;
+        const uint32_t t_o = t_row + 256 + t * D;
         float m_used = -FLT_MAX;  // maximum the exponentials are taken against (log2 domain)
         float l = 0.0f;           // running row sum
         bool ok = true;
-        unsigned char *p_row = sP + row_in_tile * 128;
+        unsigned char *p_row = sP + t * TILE_BYTES + row_in_tile * 128;
         const int sw = row_in_tile & 7;
 
         for (int j = 0; j < n_blocks && ok; ++j) {
-            const int buf = j & 1;
-            if (!mbar_wait(&s_full[buf], (j >> 1) & 1, status, 308)) { ok = false; break; }
+            // s_full(j) also tells that P_t V_{j-1} has finished: the tensor pipe runs in order.
+            if (!mbar_wait(&s_full[t], j & 1, status, 308)) { ok = false; break; }
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 0, j);
             tc_fence_after();
-            uint32_t sr[4][32];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_row + buf * BN + c * 32, sr[c]);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free[buf]);
-
             const int valid = min(BN, nkv - j * BN);
+
+            // pass 1: block maximum.  S is read again in pass 2, so few registers stay live; the
+            // TMEM load of the next 32 columns is in flight while the current ones are reduced.
             float m_blk = -FLT_MAX;
+            {
+                uint32_t buf[2][32];
+                tmem_ld_32x32(t_s, buf[0]);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld_wait();
+                    if (c < 3) tmem_ld_32x32(t_s + (c + 1) * 32, buf[(c + 1) & 1]);
+                    const uint32_t(&sr)[32] = buf[c & 1];
+                    if (valid == BN) {
+                        float m0 = m_blk, m1 = -FLT_MAX;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float v = __uint_as_float(sr[c][i]) * scale_log2;
-                    if (c * 32 + i >= valid) v = -FLT_MAX;
-                    sr[c][i] = __float_as_uint(v);
-                    m_blk = fmaxf(m_blk, v);
+                        for (int i = 0; i < 32; i += 4) {
+                            m0 = fmaxf(m0, fmaxf(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])));
+                            m1 = fmaxf(m1, fmaxf(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])));
+                        }
+                        m_blk = fmaxf(m0, m1);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i < valid) m_blk = fmaxf(m_blk, __uint_as_float(sr[i]));
+                    }
                 }
+            }
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 1, j);
+            // start pass 2's first load now; it completes under the bookkeeping below
+            uint32_t buf[2][32];
+            tmem_ld_32x32(t_s, buf[0]);
+            m_blk *= scale_log2;  // scale > 0: the maximum commutes with the scaling
             // Lazy rescale: keep the old reference maximum unless it has fallen behind by more
             // than the threshold, so that O is touched rarely.
             const bool grow = (m_blk - m_used) > RESCALE_THRESHOLD;
-            float alpha = 1.0f;
             if (j == 0) {
                 m_used = m_blk;
-            } else if (grow) {
-                alpha = fast_exp2(m_used - m_blk);
-                m_used = m_blk;
-                l *= alpha;
-            }
-            float sum = 0.0f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float p = fast_exp2(__uint_as_float(sr[c][i]) - m_used);
-                    sum += p;
-                    sr[c][i] = __float_as_uint(p);
+            } else if (__any_sync(0xffffffffu, grow)) {
+                float alpha = 1.0f;
+                if (grow) {
+                    alpha = fast_exp2(m_used - m_blk);
+                    m_used = m_blk;
+                    l *= alpha;
                 }
-            l += sum;
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(t_o + c * 32, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x32(t_o + c * 32, o);
+                }
+                tmem_st_wait();
+            }
+            const uint64_t scale2 = pk2(scale_log2, scale_log2);
+            const uint64_t negm2 = pk2(-m_used, -m_used);
 
-            // P (and O) may be touched only after P_{j-1} V_{j-1} has finished.
-            if (j > 0) {
-                if (!mbar_wait(pv_done, (j - 1) & 1, status, 309)) { ok = false; break; }
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
+            // pass 2: p = 2^(s * scale_log2 - m) on fp32x2 pairs (even pairs on the MUFU, odd pairs
+            // as a cubic on the FMA pipe), row sum, and bf16 P into shared memory in the 128-byte
+            // swizzled K-major layout (16-byte unit u of row r sits at unit u ^ (r % 8)); kv 0-63
+            // go to the first 64-column chunk of the tile, 64-127 to the second.
+            uint64_t sum2 = pk2(0.0f, 0.0f);
+            auto exp_chunk = [&](auto masked, int c, const uint32_t(&sr)[32]) {
+                uint32_t pb[16];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(t_o + c * 32, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32(t_o + c * 32, o);
+                for (int k = 0; k < 16; ++k) {
+                    const uint64_t x2 =
+                        fma2(pk2(__uint_as_float(sr[2 * k]), __uint_as_float(sr[2 * k + 1])), scale2, negm2);
+                    uint64_t e2 = (k & 1) ? poly_exp2_pair(x2) : mufu_exp2_pair(x2);
+                    float e0, e1;
+                    unpk2(e2, e0, e1);
+                    if (decltype(masked)::value) {
+                        if (c * 32 + 2 * k >= valid) e0 = 0.0f;
+                        if (c * 32 + 2 * k + 1 >= valid) e1 = 0.0f;
+                        e2 = pk2(e0, e1);
                     }
-                    tmem_st_wait();
+                    sum2 = add2(sum2, e2);
+                    pb[k] = pack_bf16(e0, e1);
                 }
-            }
-            // P row -> shared memory, bf16, 128-byte swizzle (16-byte unit u of row r lands at
-            // unit u ^ (r % 8)); kv 0-63 in the first chunk, 64-127 in the second.
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    uint4 v;
-                    v.x = pack_bf16(__uint_as_float(sr[c][8 * q + 0]), __uint_as_float(sr[c][8 * q + 1]));
-                    v.y = pack_bf16(__uint_as_float(sr[c][8 * q + 2]), __uint_as_float(sr[c][8 * q + 3]));
-                    v.z = pack_bf16(__uint_as_float(sr[c][8 * q + 4]), __uint_as_float(sr[c][8 * q + 5]));
-                    v.w = pack_bf16(__uint_as_float(sr[c][8 * q + 6]), __uint_as_float(sr[c][8 * q + 7]));
-                    const int unit = (c & 1) * 4 + q;  // 16-byte unit inside the 128-byte row
-                    *reinterpret_cast<uint4 *>(p_row + (c >> 1) * CHUNK_BYTES + ((unit ^ sw) << 4)) = v;
+                    const int unit = (c & 1) * 4 + q;
+                    *reinterpret_cast<uint4 *>(p_row + (c >> 1) * CHUNK_BYTES + ((unit ^ sw) << 4)) =
+                        make_uint4(pb[4 * q], pb[4 * q + 1], pb[4 * q + 2], pb[4 * q + 3]);
                 }
+            };
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld_wait();
+                if (c < 3) tmem_ld_32x32(t_s + (c + 1) * 32, buf[(c + 1) & 1]);
+                if (valid == BN)
+                    exp_chunk(std::false_type{}, c, buf[c & 1]);
+                else
+                    exp_chunk(std::true_type{}, c, buf[c & 1]);
+            }
+            float sum_lo, sum_hi;
+            unpk2(sum2, sum_lo, sum_hi);
+            const float sum = sum_lo + sum_hi;
+            l += sum;
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 2, j);
             fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready);
+            if (lane == 0) mbar_arrive(&sp_ready[t]);
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 3, j);
         }
 
         // ---- epilogue: O / l -> bf16 -> global ----
-        if (ok && n_blocks > 0) ok = mbar_wait(pv_done, (n_blocks - 1) & 1, status, 310);
+        if (ok && n_blocks > 0) ok = mbar_wait(&o_full[t], 0, status, 310);
         if (ok && n_blocks > 0) {
             tc_fence_after();
             const float inv = 1.0f / l;
-            const int row = q0 + row_in_tile;
+            const int row = q0 + t * BM + row_in_tile;
             const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(O) & 15) == 0);
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -302,7 +387,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, attn::TMEM_COLS);
     }
@@ -328,7 +413,7 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     GB200_CUDA_TRY(cudaFuncSetAttribute(attention_bf16_kernel,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     const float scale_log2 = scale * 1.4426950408889634f;
-    const unsigned grid = (unsigned)((nq + BM - 1) / BM);
+    const unsigned grid = (unsigned)((nq + BM * TILES - 1) / (BM * TILES));
     attention_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
         tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv, scale_log2,
         ctx->d_status);
@@ -364,6 +449,12 @@ int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void 
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
                               static_cast<cudaStream_t>(stream));
 }
+
+#ifdef GB200_ATTN_TRACE
+int gb200_attn_trace_read(long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 16 * 64);
+}
+#endif
 
 int gb200_attention_bf16_host(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K,
                               int64_t ldk, const void *V, int64_t ldv, void *O, int64_t ldo,

@@ -25,29 +25,6 @@ __device__ __forceinline__ float div3(float x) {
     return fmaf(r, rc, q);
 }
 
-// Packed fp32x2 arithmetic (sm_100 has two-wide FADD/FMUL/FFMA): the same IEEE round-to-nearest
-// operations as the scalar code above on two lanes at once, so results stay bit-identical
-// while the instruction count of the stencil halves.
-__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-    return d;
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
 __device__ __forceinline__ uint64_t div3_2(uint64_t x) {
     const uint64_t rc = pk2(0x1.555556p-2f, 0x1.555556p-2f);
     const uint64_t m3 = pk2(-3.0f, -3.0f);
@@ -192,7 +169,7 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict
 // ---------------------------------------------------------------------------------------
 template <int ROWS>
 __global__ void __launch_bounds__(128)
-blur3x3_direct2_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
+blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
                        float *__restrict__ out, int64_t out_ld, int out_rows, int out_vec) {
     const int out_cols = in_cols - 2;
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
@@ -362,14 +339,14 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
 }
 
 template <int ROWS>
-static int launch_direct2(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
+static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
                           int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream) {
     const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
     dim3 grid((unsigned)((out_cols + 511) / 512), (unsigned)((out_rows + ROWS - 1) / ROWS));
-    blur3x3_direct2_kernel<ROWS><<<grid, 128, 0, stream>>>(
+    blur3x3_reg_kernel<ROWS><<<grid, 128, 0, stream>>>(
         in, in_ld, (int)in_cols, out, out_ld, (int)out_rows,
         (aligned16(out) && out_ld % 4 == 0) ? 1 : 0);
-    return after_launch(ctx, "blur3x3_direct2_kernel");
+    return after_launch(ctx, "blur3x3_reg_kernel");
 }
 
 static int check_blur_args(const float *in, int64_t in_ld, int64_t in_rows, int64_t in_cols,
@@ -401,11 +378,11 @@ int blur_dispatch(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_row
     if (variant == 3 && tma_ok)
         return launch_tma<8, 2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream, 4);
     switch (variant) {
-        case 40: return launch_direct2<2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-        case 41: return launch_direct2<3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-        case 43: return launch_direct2<6>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-        case 44: return launch_direct2<8>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
-        default: return launch_direct2<4>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 40: return launch_reg<2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 41: return launch_reg<3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 43: return launch_reg<6>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        case 44: return launch_reg<8>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
+        default: return launch_reg<4>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
     }
 }
 
