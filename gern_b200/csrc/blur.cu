@@ -170,16 +170,23 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict
 template <int ROWS>
 __global__ void __launch_bounds__(128)
 blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
-                       float *__restrict__ out, int64_t out_ld, int out_rows, int out_vec) {
+                   float *__restrict__ out, int64_t out_ld, int out_rows, int out_vec,
+                   int in_rows_local, const float *__restrict__ halo, int64_t halo_ld) {
+    // Input rows >= in_rows_local are not in `in`: they are the rows of the next row band and
+    // are read from `halo` (which may be a peer GPU's memory; ordinary loads only).
     const int out_cols = in_cols - 2;
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
     if (c0 >= out_cols) return;
-    const int r_begin = blockIdx.y * ROWS;
+    // With a halo the block rows run bottom-up, so that the few blocks that read the (possibly
+    // remote, high-latency) halo rows start first and finish under the rest of the kernel.
+    const int by = halo != nullptr ? (gridDim.y - 1 - blockIdx.y) : blockIdx.y;
+    const int r_begin = by * ROWS;
     const int n_out = min(ROWS, out_rows - r_begin);
     const int ncol = min(4, out_cols - c0);
     const float *src = in + static_cast<int64_t>(r_begin) * in_ld + c0;
     float *dst = out + static_cast<int64_t>(r_begin) * out_ld + c0;
-    if (n_out == ROWS && c0 + 6 <= in_cols && out_vec) {
+    const bool local = r_begin + n_out + 2 <= in_rows_local;   // uniform over the block
+    if (n_out == ROWS && c0 + 6 <= in_cols && out_vec && local) {
         float4 a[ROWS + 2];
         float2 b[ROWS + 2];
 #pragma unroll
@@ -198,9 +205,13 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
         // ragged bottom or right edge, or output rows that are not 16-byte aligned
         uint64_t t0a = 0, t0b = 0, t1a = 0, t1b = 0;
         for (int r = 0; r < n_out + 2; ++r) {
+            const int gr = r_begin + r;
+            const float *rp = gr < in_rows_local
+                                  ? src + r * in_ld
+                                  : halo + static_cast<int64_t>(gr - in_rows_local) * halo_ld + c0;
             float v[6];
 #pragma unroll
-            for (int k = 0; k < 6; ++k) v[k] = (c0 + k < in_cols) ? src[r * in_ld + k] : 0.0f;
+            for (int k = 0; k < 6; ++k) v[k] = (c0 + k < in_cols) ? rp[k] : 0.0f;
             uint64_t ta, tb;
             hpass4(make_float4(v[0], v[1], v[2], v[3]), make_float2(v[4], v[5]), ta, tb);
             if (r >= 2)
@@ -338,14 +349,17 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
     return after_launch(ctx, "blur3x3_tma_kernel");
 }
 
+// `in_rows` counts the halo rows too: in holds in_rows - (halo ? 2 : 0) rows.
 template <int ROWS>
 static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
-                          int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream) {
+                      int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream,
+                      const float *halo = nullptr, int64_t halo_ld = 0) {
     const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
     dim3 grid((unsigned)((out_cols + 511) / 512), (unsigned)((out_rows + ROWS - 1) / ROWS));
     blur3x3_reg_kernel<ROWS><<<grid, 128, 0, stream>>>(
         in, in_ld, (int)in_cols, out, out_ld, (int)out_rows,
-        (aligned16(out) && out_ld % 4 == 0) ? 1 : 0);
+        (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, (int)(halo ? in_rows - 2 : in_rows), halo,
+        halo_ld);
     return after_launch(ctx, "blur3x3_reg_kernel");
 }
 
@@ -425,15 +439,12 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
     rc = check_blur_args(in, in_ld, band_rows + 2, in_cols, out, out_ld);
     if (rc) return rc < 0 ? rc : GB200_OK;
     GB200_REQUIRE(halo_ld >= in_cols, GB200_ERR_INVALID_ARG, "halo_ld smaller than the row");
-    // Rows that need only this GPU's band go through the normal path; the last two output
-    // rows read the halo and are produced by the direct kernel.
-    const int64_t body_rows = band_rows - 2;  // output rows computable without the halo
-    if (body_rows > 0) {
-        rc = blur_dispatch(ctx, in, in_ld, band_rows, in_cols, out, out_ld, stream, 0);
-        if (rc) return rc;
-    }
-    const int64_t tail_begin = body_rows > 0 ? body_rows : 0;
-    return launch_direct(ctx, in, in_ld, band_rows, halo, halo_ld, in_cols, out, out_ld, tail_begin,
+    // Aligned images: one launch of the register-staged kernel; only its last block row reads
+    // the halo.  Otherwise the generic kernel does the same with per-row pointer selection.
+    if (aligned16(in) && in_ld % 4 == 0)
+        return launch_reg<4>(ctx, in, in_ld, band_rows + 2, in_cols, out, out_ld, stream, halo,
+                             halo_ld);
+    return launch_direct(ctx, in, in_ld, band_rows, halo, halo_ld, in_cols, out, out_ld, 0,
                          band_rows, stream);
 }
 
