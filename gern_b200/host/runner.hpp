@@ -1,0 +1,243 @@
+// Runner: compile + evaluate for the B200 path, shaped after the reference's
+// (include/gern/compose/runner.h:14-46, src/codegen/runner.cpp:11-80).
+//
+// The reference's compile() lowers the Composable to C++/CUDA text, shells out to nvcc, dlopens
+// the result and keeps the hook; evaluate() checks the argument names and calls the hook.  Here
+// compile() lowers the Composable to one of the fused sm_100a kernels of libgern_b200: it strips
+// the Tile / Reduce / Stage / Global structure (checking it for legality), takes the sequence of
+// leaf calls and their data flow, and recognises
+//     matrix_multiply                                   -> gb200_gemm_f32 / gb200_gemm_bf16
+//     blur_x ; blur_y through a temporary                -> gb200_blur3x3_f32
+//     max ; subtract ; exp ; sum ; divide on one matrix  -> gb200_softmax_rows_f32
+//     matrix_multiply ; the softmax chain ; matrix_multiply through temporaries
+//                                                        -> gb200_attention_bf16
+// Anything else is a UserError: there is no generic code generator and no fallback behind this
+// Runner.  evaluate() performs the reference's argument checks (every ADT of the program must be
+// supplied by name, nothing else may be) and makes one C-ABI call.
+#pragma once
+
+#include <algorithm>
+#include <map>
+#include <set>
+#include <sstream>
+
+#include "compose.hpp"
+#include "gern_b200.h"
+#include "impl.hpp"
+
+namespace gern {
+namespace b200 {
+
+class Runner {
+public:
+    explicit Runner(Composable c) : c(std::move(c)) {}
+    // Same fields as the reference's Options (runner.h:19-26).  Only `arch` matters here: if set
+    // it must be "100a", the one architecture the library holds code for.
+    struct Options {
+        std::string filename;
+        std::string prefix = "/tmp";
+        std::string cpp_std = "c++17";
+        std::string include = "";
+        std::string ldflags = "";
+        std::string arch = "";
+    };
+
+    enum class Kernel { None, GemmF32, GemmBF16, Blur, Softmax, Attention };
+
+    void compile() { compile(Options{}); }
+    void compile(Options config) {
+        if (!config.arch.empty() && config.arch != "100a")
+            throw error::UserError("libgern_b200 holds sm_100a code only (arch=" + config.arch + ")");
+        calls.clear();
+        std::set<int> units;
+        bool in_global = false;
+        flatten(c, units, in_global);
+        if (calls.empty()) throw error::UserError("empty program");
+        lower();
+        compiled = true;
+    }
+
+    Kernel kernel() const { return plan; }
+    std::vector<std::string> argumentOrder() const { return argument_order; }
+
+    void evaluate(std::map<std::string, void *> args) {
+        if (!compiled) throw error::UserError("Please compile the pipeline first");
+        if (args.size() != argument_order.size())
+            throw error::UserError("All the arguments have not been passed! Expecting " +
+                                   std::to_string(argument_order.size()) + " args");
+        for (const auto &a : argument_order)
+            if (args.count(a) <= 0) throw error::UserError("Argument " + a + " was not passed in");
+        auto M = [&](const std::string &n) -> impl::MatrixGPU & { return *static_cast<impl::MatrixGPU *>(args.at(n)); };
+        gb200_ctx *ctx = context();
+        int rc = 0;
+        switch (plan) {
+            case Kernel::GemmF32: {
+                auto &A = M(names[0]), &B = M(names[1]), &C = M(names[2]);
+                require(A.col == B.row && C.row == A.row && C.col == B.col, "matrix_multiply: shapes do not agree");
+                // The reference's leaf accumulates into C (c += sum): keep that.
+                rc = gb200_gemm_f32(ctx, (const float *)A.data, A.lda, (const float *)B.data, B.lda,
+                                    (float *)C.data, C.lda, C.row, C.col, A.col, 1, nullptr);
+                break;
+            }
+            case Kernel::GemmBF16: {
+                auto &A = M(names[0]), &B = M(names[1]), &C = M(names[2]);
+                // B is a column-major K x N matrix: its object holds N rows of K values.
+                require(A.col == B.col && C.row == A.row && C.col == B.row, "matrix_multiply: shapes do not agree");
+                rc = gb200_gemm_bf16(ctx, A.data, A.lda, B.data, B.lda, C.data, C.lda, C.row, C.col, A.col, nullptr);
+                break;
+            }
+            case Kernel::Blur: {
+                auto &in = M(names[0]), &out = M(names[1]);
+                require(in.row >= out.row + 2 && in.col >= out.col + 2, "blur: the input must exceed the output by 2 rows and columns");
+                rc = gb200_blur3x3_f32(ctx, (const float *)in.data, in.lda, out.row + 2, out.col + 2,
+                                       (float *)out.data, out.lda, nullptr);
+                break;
+            }
+            case Kernel::Softmax: {
+                auto &in = M(names[0]), &out = M(names[1]);
+                require(in.row == out.row && in.col == out.col, "softmax: shapes do not agree");
+                rc = gb200_softmax_rows_f32(ctx, (const float *)in.data, in.lda, (float *)out.data, out.lda,
+                                            in.row, in.col, nullptr);
+                break;
+            }
+            case Kernel::Attention: {
+                auto &Q = M(names[0]), &K = M(names[1]), &V = M(names[2]), &O = M(names[3]);
+                require(Q.col == K.col && K.row == V.row && O.row == Q.row && O.col == V.col, "attention: shapes do not agree");
+                rc = gb200_attention_bf16(ctx, Q.data, Q.lda, K.data, K.lda, V.data, V.lda, O.data, O.lda,
+                                          Q.row, K.row, Q.col, scale, nullptr);
+                break;
+            }
+            default: throw error::InternalError("no kernel planned");
+        }
+        if (rc != 0) throw error::UserError(std::string("libgern_b200: ") + gb200_last_error_string());
+    }
+
+    // The reference's callers synchronise through cudaMemcpy in MatrixGPU::get(); so do ours.
+    static gb200_ctx *context() {
+        static gb200_ctx *ctx = nullptr;
+        if (!ctx && gb200_ctx_create(0, &ctx) != 0)
+            throw error::UserError(std::string("libgern_b200: ") + gb200_last_error_string());
+        return ctx;
+    }
+
+private:
+    static void require(bool ok, const char *msg) {
+        if (!ok) throw error::UserError(msg);
+    }
+
+    void flatten(const Composable &n, std::set<int> units, bool in_global) {
+        if (!n.defined()) throw error::UserError("undefined Composable in the program");
+        const Node *p = n.get();
+        switch (p->kind) {
+            case Node::Call: calls.push_back(p->call); return;
+            case Node::Computation:
+                for (const auto &ch : p->children) flatten(ch, units, in_global);
+                return;
+            case Node::Global:
+                if (in_global) throw error::UserError("Global inside Global");
+                flatten(p->children[0], units, true);
+                return;
+            case Node::Stage: flatten(p->children[0], units, in_global); return;
+            case Node::Tiled: {
+                if (p->unit != Grid::UNDEFINED) {
+                    // A grid unit can drive one loop of a nest only (composable.cpp:242-262).
+                    if (units.count(p->unit))
+                        throw error::UserError(std::string("grid unit ") + Grid::name(p->unit) + " is bound twice in one nest");
+                    if (!in_global) throw error::UserError("a grid unit can only be bound inside Global()");
+                    units.insert(p->unit);
+                }
+                if (!p->reduce && !p->member.adt.defined()) throw error::UserError("Tile needs an ADT field");
+                if (!p->tile.defined()) throw error::UserError("tile variable has no name");
+                flatten(p->children[0], units, in_global);
+                // the tiled field must belong to an output of the body (Tile) -- composable.cpp:142-192
+                if (!p->reduce) {
+                    bool found = false;
+                    for (const auto &cl : calls) found = found || cl.output == p->member.adt;
+                    if (!found)
+                        throw error::UserError("Tile(" + p->member.adt.getName() + "[\"" + p->member.field +
+                                               "\"]): the data type is not produced by the tiled computation");
+                }
+                return;
+            }
+        }
+    }
+
+    bool isChain(size_t at, AbstractDataTypePtr &in, AbstractDataTypePtr &out) const {
+        // max(in -> m); subtract(m, in -> t1); exp(t1 -> t2); sum(t2 -> s); divide(s, t2 -> out)
+        if (at + 5 > calls.size()) return false;
+        const auto &mx = calls[at], &sb = calls[at + 1], &ex = calls[at + 2], &sm = calls[at + 3], &dv = calls[at + 4];
+        if (mx.op != Op::MaxRow || sb.op != Op::SubstractVec || ex.op != Op::ExpMatrix || sm.op != Op::SumRow ||
+            dv.op != Op::DivideVec)
+            return false;
+        in = mx.inputs[0];
+        const bool flow = sb.inputs[0] == mx.output && sb.inputs[1] == in && ex.inputs[0] == sb.output &&
+                          sm.inputs[0] == ex.output && dv.inputs[0] == sm.output && dv.inputs[1] == ex.output;
+        if (!flow) return false;
+        out = dv.output;
+        return true;
+    }
+
+    void lower() {
+        names.clear();
+        auto f32 = [](const AbstractDataTypePtr &a) { return a->getDatatype() == Datatype::Float32; };
+        if (calls.size() == 1 && calls[0].op == Op::MatrixMultiply) {
+            const auto &A = calls[0].inputs[0], &B = calls[0].inputs[1], &C = calls[0].output;
+            if (f32(A) && f32(B) && f32(C)) {
+                if (B->getLayout() != Layout::RowMajor) throw error::UserError("fp32 matrix_multiply takes a row-major B");
+                plan = Kernel::GemmF32;
+            } else if (!f32(A) && !f32(B) && !f32(C)) {
+                if (B->getLayout() != Layout::ColMajor) throw error::UserError("bf16 matrix_multiply takes a column-major B");
+                plan = Kernel::GemmBF16;
+            } else {
+                throw error::UserError("matrix_multiply: mixed element types");
+            }
+            names = {A.getName(), B.getName(), C.getName()};
+        } else if (calls.size() == 2 && calls[0].op == Op::BlurX && calls[1].op == Op::BlurY) {
+            if (!(calls[1].inputs[0] == calls[0].output))
+                throw error::UserError("blur_y must consume the output of blur_x");
+            for (const auto &cl : calls) {
+                auto it = cl.template_args.find("stride");
+                if (it == cl.template_args.end() || it->second.getInt64Val() != 3)
+                    throw error::UserError("this library fuses blur_x/blur_y with stride 3 only");
+            }
+            plan = Kernel::Blur;
+            names = {calls[0].inputs[0].getName(), calls[1].output.getName()};
+        } else if (calls.size() == 5) {
+            AbstractDataTypePtr in, out;
+            if (!isChain(0, in, out)) throw error::UserError("unrecognised 5-call pipeline (expected the softmax chain)");
+            plan = Kernel::Softmax;
+            names = {in.getName(), out.getName()};
+        } else if (calls.size() == 7 && calls[0].op == Op::MatrixMultiply && calls[6].op == Op::MatrixMultiply) {
+            AbstractDataTypePtr in, out;
+            if (!isChain(1, in, out) || !(in == calls[0].output) || !(calls[6].inputs[0] == out))
+                throw error::UserError("unrecognised 7-call pipeline (expected matmul ; softmax ; matmul)");
+            const auto &Q = calls[0].inputs[0], &K = calls[0].inputs[1], &V = calls[6].inputs[1], &O = calls[6].output;
+            if (f32(Q) || f32(K) || f32(V) || f32(O)) throw error::UserError("the fused chain takes BFloat16 Q, K, V, O");
+            if (K->getLayout() != Layout::ColMajor) throw error::UserError("the fused chain takes K as the column-major operand of Q K^T");
+            plan = Kernel::Attention;
+            scale = calls[0].scale;
+            names = {Q.getName(), K.getName(), V.getName(), O.getName()};
+        } else {
+            std::ostringstream os;
+            os << "no fused sm_100a kernel for this pipeline:";
+            for (const auto &cl : calls) os << " " << opName(cl.op);
+            throw error::UserError(os.str());
+        }
+        // Argument order = ADTs sorted by name, as the reference orders them (codegen.cpp:139-198).
+        argument_order = names;
+        std::sort(argument_order.begin(), argument_order.end());
+        std::set<std::string> uniq(argument_order.begin(), argument_order.end());
+        if (uniq.size() != argument_order.size()) throw error::UserError("two arguments share a name");
+    }
+
+    Composable c;
+    std::vector<FunctionCall> calls;
+    Kernel plan = Kernel::None;
+    std::vector<std::string> names;           // in kernel-argument order
+    std::vector<std::string> argument_order;  // sorted, as evaluate() expects them
+    float scale = 1.0f;
+    bool compiled = false;
+};
+
+}  // namespace b200
+}  // namespace gern
