@@ -31,6 +31,7 @@ SIGNATURES = {
     "gb200_launch_count": None,
     "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
     "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
+    "gb200_gemm_bf16_splitk": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
     "gb200_softmax_rows_f32": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
     "gb200_softmax_rows_f32_variant": [_vp, _i64, _vp, _i64, _i64, _i64, _vp, _int],
     "gb200_blur3x3_f32": [_vp, _i64, _i64, _i64, _vp, _i64, _vp],
@@ -127,10 +128,15 @@ class Context:
         _check(lib.gb200_gemm_f32(self.handle, _ptr(A), _ld(A), _ptr(B), _ld(B), _ptr(C), _ld(C), M, N, K,
                                   int(bool(accumulate)), _stream(stream)), "gb200_gemm_f32")
 
-    def gemm_bf16(self, A, Bt, C, stream=None):
+    def gemm_bf16(self, A, Bt, C, stream=None, splits=None):
         """A: (M,K) bf16; Bt: (N,K) bf16 (column-major B); C: (M,N) bf16."""
         M, K = A.shape
         N = Bt.shape[0]
+        if splits is not None:
+            _check(lib.gb200_gemm_bf16_splitk(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C),
+                                              _ld(C), M, N, K, _stream(stream), int(splits)),
+                   "gb200_gemm_bf16_splitk")
+            return
         _check(lib.gb200_gemm_bf16(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N,
                                    K, _stream(stream)), "gb200_gemm_bf16")
 

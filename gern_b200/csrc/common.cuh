@@ -73,6 +73,9 @@ struct gb200_ctx {
     // staging of the _host entry points (grown on demand, freed at destroy)
     void *stage[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t stage_bytes[4] = {0, 0, 0, 0};
+    // scratch of kernels that need global memory beyond their operands (split-K slabs)
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
     cudaStream_t copy_stream[2] = {nullptr, nullptr};
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
 };
@@ -89,6 +92,8 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
 int enter(gb200_ctx *ctx);
 // Grows staging slot `slot` to at least `bytes`.
 int stage_reserve(gb200_ctx *ctx, int slot, size_t bytes);
+// Grows the context's kernel workspace to at least `bytes`.
+int workspace_reserve(gb200_ctx *ctx, size_t bytes);
 // Checks the launch that was just issued and counts it.
 int after_launch(gb200_ctx *ctx, const char *what);
 

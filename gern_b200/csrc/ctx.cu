@@ -47,6 +47,18 @@ int stage_reserve(gb200_ctx *ctx, int slot, size_t bytes) {
     return GB200_OK;
 }
 
+int workspace_reserve(gb200_ctx *ctx, size_t bytes) {
+    if (ctx->workspace_bytes >= bytes) return GB200_OK;
+    if (ctx->workspace) {
+        GB200_CUDA_TRY(cudaFree(ctx->workspace));   // cudaFree waits for work that still uses it
+        ctx->workspace = nullptr;
+        ctx->workspace_bytes = 0;
+    }
+    GB200_CUDA_TRY(cudaMalloc(&ctx->workspace, bytes));
+    ctx->workspace_bytes = bytes;
+    return GB200_OK;
+}
+
 int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int elem_bytes,
                 uint64_t d0, uint64_t d1, uint64_t stride1_bytes, uint32_t b0, uint32_t b1,
                 CUtensorMapSwizzle swizzle, CUtensorMap *out) {
@@ -151,6 +163,7 @@ int gb200_ctx_destroy(gb200_ctx *ctx) {
         if (ctx->copy_stream[i]) cudaStreamDestroy(ctx->copy_stream[i]);
     for (int i = 0; i < 4; ++i)
         if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
+    if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->d_status) cudaFree(ctx->d_status);
     delete ctx;
     return GB200_OK;

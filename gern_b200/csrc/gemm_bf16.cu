@@ -14,7 +14,9 @@
 //     into one of two 256-column fp32 accumulators in TMEM and releases ring slots with
 //     tcgen05.commit;
 //   * warps 2-5 drain the finished accumulator with tcgen05.ld, round to bf16 and store C,
-//     overlapping the next tile's main loop (the other TMEM accumulator).
+//     overlapping the next tile's main loop (the other TMEM accumulator);
+//   * problems with too few tiles to fill the SMs are split along K: each (tile, split) item
+//     writes an fp32 partial slab to a workspace and a small second kernel sums the slabs.
 // Every wait is bounded; a wait that runs out records a code in the context's status word and
 // the kernel winds down (TMEM is always freed).
 #include "common.cuh"
@@ -46,7 +48,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
-                    int64_t ldc, int M, int N, int K, int *status) {
+                    int64_t ldc, int M, int N, int K, int splits, float *__restrict__ ws,
+                    int *status) {
     using namespace gemm;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -60,8 +63,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-    const int n_tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
+    // Split-K: a work item is (tile, split); split s reduces k blocks [s*kb_per, (s+1)*kb_per)
+    // into an fp32 slab of the workspace, and a second kernel sums the slabs into C.
+    const int kb_per = (k_blocks + splits - 1) / splits;
+    const int n_tiles = tiles_m * tiles_n * splits;   // work items
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_a);
@@ -92,8 +98,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 int tm, tn;
-                tile_coords(t, tiles_m, tiles_n, tm, tn);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
+                const int kb_begin = (t % splits) * kb_per, kb_end = min(k_blocks, kb_begin + kb_per);
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&empty[s], ph ^ 1, status, 201)) { ok = false; break; }
@@ -116,7 +123,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (!mbar_wait(&acc_empty[buf], acc_ph ^ 1, status, 202)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int kb_begin = (t % splits) * kb_per, kb_end = min(k_blocks, kb_begin + kb_per);
+                for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&full[s], ph, status, 203)) { ok = false; break; }
@@ -128,7 +136,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     for (int k = 0; k < BK / 16; ++k) {
                         // 16 bf16 = 32 bytes along K inside the 128-byte swizzle row
                         umma_f16_ss(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
-                                    (kb | k) != 0 ? 1u : 0u);
+                                    (kb != kb_begin || k != 0) ? 1u : 0u);
                     }
                     umma_commit(&empty[s]);  // slot is free once these MMAs have read it
                 }
@@ -143,7 +151,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
             int tm, tn;
-            tile_coords(t, tiles_m, tiles_n, tm, tn);
+            tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
+            const int split = t % splits;
+            const bool empty_range = split * kb_per >= k_blocks;   // nothing was accumulated
             const int buf = tile_it & 1;
             const uint32_t acc_ph = (tile_it >> 1) & 1;
             if (!mbar_wait(&acc_full[buf], acc_ph, status, 204)) { ok = false; break; }
@@ -157,7 +167,23 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tmem_ld_32x32(taddr + ch * 32, r);
                 tmem_ld_wait();
                 const int col = tn * BN + ch * 32;
-                if (row < M && col < N) {
+                if (splits > 1) {
+                    // fp32 partial sums into slab `split` of the workspace ([splits][M][N])
+                    if (row < M && col < N) {
+                        float *dst = ws + (static_cast<int64_t>(split) * M + row) * N + col;
+                        if ((N & 3) == 0 && col + 32 <= N) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q)
+                                *reinterpret_cast<uint4 *>(dst + 4 * q) =
+                                    empty_range ? make_uint4(0, 0, 0, 0)
+                                                : make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < N) dst[j] = empty_range ? 0.0f : __uint_as_float(r[j]);
+                        }
+                    }
+                } else if (row < M && col < N) {
                     __nv_bfloat16 *dst = C + static_cast<int64_t>(row) * ldc + col;
                     if (vec_ok && col + 32 <= N) {
 #pragma unroll
@@ -190,6 +216,39 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
+// Second step of split-K: C = bf16(sum over slabs), one thread per 4 adjacent columns.
+__global__ void __launch_bounds__(256)
+gemm_splitk_reduce_kernel(const float *__restrict__ ws, int splits, __nv_bfloat16 *__restrict__ C,
+                          int64_t ldc, int M, int N) {
+    const int64_t groups_per_row = (N + 3) / 4;
+    const int64_t total = static_cast<int64_t>(M) * groups_per_row;
+    const int64_t slab = static_cast<int64_t>(M) * N;
+    const bool vec = (N & 3) == 0 && (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 7) == 0;
+    for (int64_t g = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; g < total;
+         g += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = g / groups_per_row;
+        const int col = static_cast<int>(g % groups_per_row) * 4;
+        const float *src = ws + row * N + col;
+        if (vec) {
+            float4 acc = *reinterpret_cast<const float4 *>(src);
+            for (int s = 1; s < splits; ++s) {
+                const float4 v = *reinterpret_cast<const float4 *>(src + s * slab);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            uint2 out;
+            out.x = pack_bf16(acc.x, acc.y);
+            out.y = pack_bf16(acc.z, acc.w);
+            *reinterpret_cast<uint2 *>(C + row * ldc + col) = out;
+        } else {
+            for (int j = 0; j < 4 && col + j < N; ++j) {
+                float acc = src[j];
+                for (int s = 1; s < splits; ++s) acc += src[j + s * slab];
+                C[row * ldc + col + j] = __float2bfloat16_rn(acc);
+            }
+        }
+    }
+}
+
 // Fallback for operands the TMA path cannot take (pitch or base not 16-byte aligned):
 // plain CUDA-core kernel, fp32 accumulate in ascending k.
 __global__ void __launch_bounds__(256)
@@ -216,8 +275,20 @@ gemm_bf16_simple_kernel(const __nv_bfloat16 *__restrict__ A, int64_t lda,
 int check_gemm_args(const void *A, int64_t lda, const void *B, int64_t ldb, void *C, int64_t ldc,
                     int64_t M, int64_t N, int64_t K, bool b_colmajor);
 
+// How many K splits to use: only when the tiles alone leave most SMs idle and K is long enough
+// (>= 2048) to pay for the second launch (measured: 512x512x8192 44 -> 19 us, 1024^3 13 -> 17 us);
+// never fewer than 8 k-blocks (512 columns of K) per split, at most 16.
+int pick_splits(int64_t n_tiles, int64_t k_blocks, int sm_count) {
+    if (n_tiles * 2 > sm_count || k_blocks < 32) return 1;
+    int64_t s = sm_count / n_tiles;
+    if (s > k_blocks / 8) s = k_blocks / 8;
+    if (s > 16) s = 16;
+    return s < 2 ? 1 : (int)s;
+}
+
 int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
-                       void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+                       void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream,
+                       int forced_splits = 0) {
     using namespace gemm;
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     const bool tc_ok = ctx->encode_tiled && al16(A) && al16(B) && lda % 8 == 0 && ldb % 8 == 0 &&
@@ -237,12 +308,28 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
                      (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
     if (rc) return rc;
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-    const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
+    const int splits = forced_splits > 0 ? forced_splits : pick_splits(n_tiles, (K + BK - 1) / BK, ctx->sm_count);
+    float *ws = nullptr;
+    if (splits > 1) {
+        rc = workspace_reserve(ctx, (size_t)splits * M * N * sizeof(float));
+        if (rc) return rc;
+        ws = static_cast<float *>(ctx->workspace);
+    }
+    const int64_t items = n_tiles * splits;
+    const int grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
     GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     gemm_bf16_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
-        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, ctx->d_status);
-    return after_launch(ctx, "gemm_bf16_tc_kernel");
+        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, splits, ws,
+        ctx->d_status);
+    rc = after_launch(ctx, "gemm_bf16_tc_kernel");
+    if (rc || splits == 1) return rc;
+    const int64_t groups = M * ((N + 3) / 4);
+    int64_t blocks = (groups + 255) / 256;
+    if (blocks > (int64_t)ctx->sm_count * 8) blocks = (int64_t)ctx->sm_count * 8;
+    gemm_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+        ws, splits, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N);
+    return after_launch(ctx, "gemm_splitk_reduce_kernel");
 }
 
 }  // namespace gb200
@@ -259,6 +346,20 @@ int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, i
     if (rc) return rc < 0 ? rc : GB200_OK;
     return gemm_bf16_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K,
                               static_cast<cudaStream_t>(stream));
+}
+
+// Test / benchmark hook: same contract with the number of K splits chosen by the caller
+// (0 = let the library pick, 1 = no split).
+int gb200_gemm_bf16_splitk(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                           void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream,
+                           int splits) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    GB200_REQUIRE(splits >= 0 && splits <= 64, GB200_ERR_INVALID_ARG, "splits out of range");
+    return gemm_bf16_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K,
+                              static_cast<cudaStream_t>(stream), splits);
 }
 
 int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,

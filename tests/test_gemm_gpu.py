@@ -97,6 +97,29 @@ def test_bf16_against_oracle(ctx, oracle, mnk):
     assert frob(got, want) <= 3e-3
 
 
+@pytest.mark.parametrize("mnk,splits", [((256, 512, 2048), 0), ((256, 512, 2048), 1), ((256, 512, 2048), 2),
+                                        ((256, 512, 2048), 5), ((130, 258, 1100), 3), ((128, 256, 8192), 16),
+                                        ((100, 203, 1024), 4), ((128, 256, 64), 4)])
+def test_bf16_split_k(ctx, oracle, mnk, splits):
+    """K split into slabs of fp32 partial sums (workspace) + reduce kernel; 0 = library's choice."""
+    m, n, k = mnk
+    g = torch.Generator(device="cuda").manual_seed(m + n + k + splits)
+    a = (torch.randn((m, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm_bf16(a, b, c, splits=splits)
+    ctx.sync()
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.gemm_bf16(np.ascontiguousarray(bits(a)), np.ascontiguousarray(bits(b)))
+    oracle.set_threads(1)
+    assert frob(c.float().cpu().numpy(), want) <= 3e-3
+    # a second call reuses the workspace and must not depend on what the first left there
+    c2 = torch.zeros_like(c)
+    ctx.gemm_bf16(a, b, c2, splits=splits)
+    ctx.sync()
+    assert torch.equal(c, c2)
+
+
 def test_bf16_unaligned_falls_to_simple_kernel(ctx, oracle):
     a, b, c = run_bf16(ctx, 70, 90, 50, seed=1, pad=3)   # pitch not a multiple of 8 elements
     want = oracle.gemm_bf16(np.ascontiguousarray(bits(a.contiguous())), np.ascontiguousarray(bits(b.contiguous())))
