@@ -32,6 +32,7 @@ SIGNATURES = {
     "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
     "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
     "gb200_gemm_bf16_splitk": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
+    "gb200_gemm_bf16_splitk_static": None,
     "gb200_softmax_rows_f32": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
     "gb200_softmax_rows_f32_variant": [_vp, _i64, _vp, _i64, _i64, _i64, _vp, _int],
     "gb200_blur3x3_f32": [_vp, _i64, _i64, _i64, _vp, _i64, _vp],
@@ -54,6 +55,8 @@ lib.gb200_last_error_string.restype = ctypes.c_char_p
 lib.gb200_version.restype = ctypes.c_char_p
 lib.gb200_launch_count.argtypes = [_vp]
 lib.gb200_launch_count.restype = _i64
+lib.gb200_gemm_bf16_splitk_static.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]
+lib.gb200_gemm_bf16_splitk_static.restype = _int
 for _name, _args in SIGNATURES.items():
     if _args is not None and hasattr(lib, _name):
         getattr(lib, _name).argtypes = [_vp] + _args
@@ -93,6 +96,14 @@ def _ld(t) -> int:
         return t.strides[0] // t.itemsize
     assert t.stride(1) == 1, "rows must be contiguous"
     return t.stride(0)
+
+
+def gemm_bf16_splitk_static(A, Bt, C, splits=0, stream=None):
+    """Context-free, allocation-free split-K GEMM on the current device (see gern_b200.h)."""
+    M, K = A.shape
+    N = Bt.shape[0]
+    _check(lib.gb200_gemm_bf16_splitk_static(_ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N, K,
+                                             int(splits), _stream(stream)), "gb200_gemm_bf16_splitk_static")
 
 
 class Context:

@@ -362,6 +362,130 @@ int gb200_gemm_bf16_splitk(gb200_ctx *ctx, const void *A, int64_t lda, const voi
                               static_cast<cudaStream_t>(stream), splits);
 }
 
+// ---- split-K GEMM for callers that must not allocate --------------------------------------
+//
+// Same kernels as gb200_gemm_bf16 with K splits, but the fp32 slab workspace and the status word
+// live in the two file-scope device arrays below instead of memory owned by a gb200_ctx, and no
+// context is needed at all.  It serves host code that is not allowed to reach the CUDA allocator
+// at the point where it needs a GEMM: a latency-critical serving loop (cudaMalloc and cudaFree
+// synchronise the whole device), a process whose device memory has been handed in full to
+// another allocator so that cudaMalloc would fail, or a callback that runs where allocation
+// calls are forbidden.  The price is a fixed capacity: kStaticWsFloats floats (16 MiB), which
+// every GPU that loads this library keeps reserved until the process exits.
+constexpr size_t kStaticWsFloats = 4u * 1024u * 1024u;
+static __device__ __align__(256) float g_static_ws[kStaticWsFloats];
+static __device__ __align__(256) int g_static_status[64];
+
+namespace {
+struct StaticDeviceState {
+    bool ready = false;
+    float *ws = nullptr;        // device address of g_static_ws on this device
+    int *status = nullptr;      // device address of g_static_status on this device
+    int sm_count = 0;
+    gb200::EncodeTiledFn encode = nullptr;
+};
+constexpr int kMaxDevices = 64;
+StaticDeviceState g_static_state[kMaxDevices];
+std::mutex g_static_mu;
+
+// In host code `g_static_ws` names a host-side shadow of the array, not device memory; the
+// device address has to be asked for, per device, with that device current.
+int static_setup(int device, StaticDeviceState **out) {
+    GB200_REQUIRE(device >= 0 && device < kMaxDevices, GB200_ERR_UNSUPPORTED,
+                  "device ordinal %d beyond the %d this entry point tracks", device, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    StaticDeviceState &st = g_static_state[device];
+    if (!st.ready) {
+        void *p = nullptr;
+        GB200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_ws));
+        st.ws = static_cast<float *>(p);
+        GB200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_status));
+        st.status = static_cast<int *>(p);
+        int major = 0;
+        GB200_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        GB200_REQUIRE(major == 10, GB200_ERR_NO_DEVICE, "device %d is not sm_100", device);
+        GB200_CUDA_TRY(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, device));
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        GB200_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        GB200_REQUIRE(q == cudaDriverEntryPointSuccess && fn != nullptr, GB200_ERR_NO_DEVICE,
+                      "cuTensorMapEncodeTiled is not available from this driver");
+        st.encode = reinterpret_cast<gb200::EncodeTiledFn>(fn);
+        GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            gemm::SMEM_BYTES));
+        st.ready = true;
+    }
+    *out = &st;
+    return GB200_OK;
+}
+
+int encode_bf16_map(const StaticDeviceState &st, const void *ptr, uint64_t inner, uint64_t rows,
+                    uint64_t pitch_bytes, uint32_t box_rows, CUtensorMap *tm) {
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)gemm::BK, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult rc = st.encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(ptr), dims,
+                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    GB200_REQUIRE(rc == CUDA_SUCCESS, GB200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", (int)rc);
+    return GB200_OK;
+}
+}  // namespace
+
+int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int64_t ldb, void *C,
+                                  int64_t ldc, int64_t M, int64_t N, int64_t K, int splits,
+                                  void *stream_) {
+    using namespace gemm;
+    int rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    GB200_REQUIRE(K > 0, GB200_ERR_INVALID_ARG, "K must be positive");
+    GB200_REQUIRE(splits >= 0 && splits <= 16, GB200_ERR_INVALID_ARG, "splits must be 0 (choose) .. 16");
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    GB200_REQUIRE(al16(A) && al16(B) && lda % 8 == 0 && ldb % 8 == 0, GB200_ERR_UNSUPPORTED,
+                  "operands need 16-byte aligned bases and pitches (TMA)");
+    int device = 0;
+    GB200_CUDA_TRY(cudaGetDevice(&device));
+    StaticDeviceState *st = nullptr;
+    rc = static_setup(device, &st);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int64_t k_blocks = (K + BK - 1) / BK;
+    if (splits == 0) splits = pick_splits(n_tiles, k_blocks, st->sm_count);
+    const size_t need = splits > 1 ? (size_t)splits * (size_t)M * (size_t)N : 0;
+    GB200_REQUIRE(need <= kStaticWsFloats, GB200_ERR_TOO_LARGE,
+                  "splits * M * N = %llu floats exceeds the fixed workspace of %llu floats (16 MiB); "
+                  "use fewer splits or gb200_gemm_bf16 with a context",
+                  (unsigned long long)need, (unsigned long long)kStaticWsFloats);
+    CUtensorMap ta, tb;
+    rc = encode_bf16_map(*st, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BM, &ta);
+    if (rc) return rc;
+    rc = encode_bf16_map(*st, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BN, &tb);
+    if (rc) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int64_t items = n_tiles * splits;
+    const int grid = (int)(items < st->sm_count ? items : st->sm_count);
+    // Every (tile, split) item overwrites its whole region of the slabs, so nothing left in the
+    // array by an earlier call is ever read; the status word is only ever set, never relied on.
+    gemm_bf16_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, splits,
+        splits > 1 ? st->ws : nullptr, st->status);
+    cudaError_t err = cudaPeekAtLastError();
+    GB200_REQUIRE(err == cudaSuccess, GB200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(err));
+    if (splits > 1) {
+        const int64_t groups = M * ((N + 3) / 4);
+        int64_t blocks = (groups + 255) / 256;
+        if (blocks > (int64_t)st->sm_count * 8) blocks = (int64_t)st->sm_count * 8;
+        gemm_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+            st->ws, splits, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N);
+        err = cudaPeekAtLastError();
+        GB200_REQUIRE(err == cudaSuccess, GB200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(err));
+    }
+    return GB200_OK;
+}
+
 int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K) {
     int rc = enter(ctx);

@@ -79,6 +79,23 @@ int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, 
 int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                     void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream);
 
+/* Split-K bf16 GEMM that allocates nothing and needs no context (same operand conventions as
+ * gb200_gemm_bf16; `splits` = 1..16, or 0 to let the library choose).  It has no counterpart in
+ * the reference.  It is for callers that cannot call cudaMalloc where they need the product: a
+ * serving loop that must not take the device-wide synchronisation an allocation implies, a
+ * process whose device memory already belongs entirely to another allocator, or a callback in
+ * which allocation calls are not permitted.  The fp32 partial-sum workspace is a fixed array of
+ * 4 Mi floats (16 MiB) inside the library, resident on every GPU that loads it until the process
+ * exits; a request with splits * M * N beyond that returns GB200_ERR_TOO_LARGE.  The first call
+ * on each device looks up the array's device address and sets kernel attributes: make that call
+ * once, with the device current, before any stream capture begins.  All calls share the one
+ * array: two calls whose kernels may overlap on the GPU (different streams) race on it; calls
+ * on one stream are safe, and nothing a previous call left in the array is ever read.  Runs on
+ * the calling thread's current device; does not synchronise. */
+int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int64_t ldb, void *C,
+                                  int64_t ldc, int64_t M, int64_t N, int64_t K, int splits,
+                                  void *stream);
+
 /* ---- row softmax ---------------------------------------------------------------------- */
 
 /* out(i,:) = exp(in(i,:) - max_j in(i,j)) / sum_j exp(in(i,j) - max_j in(i,j)), fp32.
