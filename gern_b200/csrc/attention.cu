@@ -12,12 +12,12 @@
 // One CTA owns two 128-row tiles of Q.  Warp 9 streams K and V blocks through one 3-slot TMA
 // ring (K_0 V_0 K_1 V_1 ...); warp 8 issues tcgen05.mma in the order P_t V_j, Q_t K_{j+1}^T for
 // tile t = 0, 1, so that while one tile's S is in the softmax the tensor pipe works on the other
-// tile; warps 0-3 (tile 0) and 4-7 (tile 1) own one row each: they read S_t from TMEM twice
-// (maximum, then exponentials; few registers stay live), update max/sum, write P_t to shared
+// tile; warps 0-3 (tile 0) and 4-7 (tile 1) own one row each: they read S_t from TMEM with all
+// loads in flight at once (a TMEM round trip costs a few hundred cycles), update max/sum, write P_t to shared
 // memory in the 128-byte-swizzled K-major layout the MMA reads, rescale O_t in TMEM when the
-// running maximum has grown by more than 2^8, and at the end normalise and store O.  Half of
-// the exponentials run on the MUFU and half as a cubic on the FMA pipe, because at this shape
-// the 16-per-clock MUFU is as scarce as the tensor pipe.  Every wait is bounded and reports
+// running maximum has grown by more than 2^8, and at the end normalise and store O.  P is packed
+// to bf16 with integer adds and a byte permute, because the conversion instruction shares the
+// 16-lane unit the exponentials keep busy.  Every wait is bounded and reports
 // through the status word.
 #include <float.h>
 
@@ -39,6 +39,14 @@ constexpr int SMEM_BYTES = (2 * TILES + KV_SLOTS) * TILE_BYTES + 1024 + 256;
 constexpr uint32_t TMEM_COLS = 512;        // S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512)
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 }  // namespace attn
+
+// Which fp32x2 pairs take their exponential on the FMA pipe instead of the MUFU: pair k does when
+// (k & GB200_POLY_AND) == GB200_POLY_AND (1: every second pair, 3: every fourth, 7: every eighth,
+// 255: none).  Measured on B200 at 32768 x 4096 x 128: 89 / 85 / 82.5 / 82.9 us, so the default
+// keeps every exponential on the MUFU; the cubic stays available for shapes where it pays.
+#ifndef GB200_POLY_AND
+#define GB200_POLY_AND 255
+#endif
 
 #ifdef GB200_ATTN_TRACE
 // Debug-only timeline (compiled out of the library): CTA 0 records clock64() at a few points.
@@ -80,6 +88,12 @@ __device__ __forceinline__ uint64_t poly_exp2_pair(uint64_t x2) {
     p0 = __int_as_float(__float_as_int(t0) * 0x800000 + __float_as_int(p0));
     p1 = __int_as_float(__float_as_int(t1) * 0x800000 + __float_as_int(p1));
     return pk2(p0, p1);
+}
+// Two non-negative finite fp32 values -> two bf16 (round half up) in one word, on the integer
+// pipe.  The F2FP conversion instruction shares the 16-lane-per-clock unit with the MUFU, which
+// the exponentials already saturate; two integer adds and a byte permute do not.
+__device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 __device__ __forceinline__ uint64_t mufu_exp2_pair(uint64_t x2) {
     float x0, x1;
@@ -243,37 +257,38 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             tc_fence_after();
             const int valid = min(BN, nkv - j * BN);
 
-            // pass 1: block maximum.  S is read again in pass 2, so few registers stay live; the
-            // TMEM load of the next 32 columns is in flight while the current ones are reduced.
+            // pass 1: row maximum of the block.  All four TMEM loads are in flight at once (a TMEM
+            // round trip costs a few hundred cycles); the 128 values are dropped again so that the
+            // exponential pass below has registers left for instruction-level parallelism.
             float m_blk = -FLT_MAX;
             {
-                uint32_t buf[2][32];
-                tmem_ld_32x32(t_s, buf[0]);
+            uint32_t sr[4][32];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld_wait();
-                    if (c < 3) tmem_ld_32x32(t_s + (c + 1) * 32, buf[(c + 1) & 1]);
-                    const uint32_t(&sr)[32] = buf[c & 1];
-                    if (valid == BN) {
-                        float m0 = m_blk, m1 = -FLT_MAX;
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sr[c]);
+            tmem_ld_wait();
+            if (valid == BN) {
+                float m0 = -FLT_MAX, m1 = -FLT_MAX;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            m0 = fmaxf(m0, fmaxf(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])));
-                            m1 = fmaxf(m1, fmaxf(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])));
-                        }
-                        m_blk = fmaxf(m0, m1);
-                    } else {
+                for (int c = 0; c < 4; ++c)
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i < valid) m_blk = fmaxf(m_blk, __uint_as_float(sr[i]));
+                    for (int i = 0; i < 32; i += 4) {
+                        m0 = fmaxf(m0, fmaxf(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])));
+                        m1 = fmaxf(m1, fmaxf(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])));
                     }
-                }
+                m_blk = fmaxf(m0, m1);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i < valid) m_blk = fmaxf(m_blk, __uint_as_float(sr[c][i]));
             }
-            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 1, j);
-            // start pass 2's first load now; it completes under the bookkeeping below
+            }
+            // pass 2's first load: in flight during the bookkeeping below
             uint32_t buf[2][32];
             tmem_ld_32x32(t_s, buf[0]);
             m_blk *= scale_log2;  // scale > 0: the maximum commutes with the scaling
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 1, j);
             // Lazy rescale: keep the old reference maximum unless it has fallen behind by more
             // than the threshold, so that O is touched rarely.
             const bool grow = (m_blk - m_used) > RESCALE_THRESHOLD;
@@ -312,7 +327,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 for (int k = 0; k < 16; ++k) {
                     const uint64_t x2 =
                         fma2(pk2(__uint_as_float(sr[2 * k]), __uint_as_float(sr[2 * k + 1])), scale2, negm2);
-                    uint64_t e2 = (k & 1) ? poly_exp2_pair(x2) : mufu_exp2_pair(x2);
+                    uint64_t e2 = ((k & GB200_POLY_AND) == GB200_POLY_AND) ? poly_exp2_pair(x2) : mufu_exp2_pair(x2);
                     float e0, e1;
                     unpk2(e2, e0, e1);
                     if (decltype(masked)::value) {
@@ -321,7 +336,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         e2 = pk2(e0, e1);
                     }
                     sum2 = add2(sum2, e2);
-                    pb[k] = pack_bf16(e0, e1);
+                    pb[k] = pack_bf16_alu(e0, e1);
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {

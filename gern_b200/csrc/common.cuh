@@ -102,9 +102,17 @@ int after_launch(gb200_ctx *ctx, const char *what);
 // ---------------------------------------------------------------------------------------
 #ifdef __CUDACC__
 
-// Upper bound on polls of any mbarrier wait.  Past it the waiting thread records a status
-// code and leaves the wait, so that a protocol error ends the kernel instead of hanging it.
-constexpr uint32_t kSpinLimit = 4u * 1000u * 1000u;
+// Upper bound on any mbarrier wait, in wall-clock time: a single try_wait may itself block for a
+// hardware-defined while, so polls are not a usable unit.  Past the limit the waiting thread
+// records a status code and leaves the wait, so that a protocol error ends the kernel (in a
+// second or two) instead of hanging it.
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;   // 1 s
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -139,8 +147,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (after writing `code` to *status) if the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    // fast path: a few polls without touching the timer
+    for (int i = 0; i < 64; ++i)
         if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    while (true) {
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
     }
     if (status) atomicExch(status, code);
     return false;
@@ -251,6 +265,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
           "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
           "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
           "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+// 32 lanes x 16 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
 }
