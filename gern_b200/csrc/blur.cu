@@ -456,7 +456,13 @@ int gb200_blur3x3_f32_host(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
     if (rc) return rc < 0 ? rc : GB200_OK;
     const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
     // Device images are packed with a pitch rounded up to 4 floats so that the TMA path applies.
-    const int64_t d_in_ld = (in_cols + 3) / 4 * 4, d_out_ld = (out_cols + 3) / 4 * 4;
+    // When the host pitch is 16-byte friendly and only slightly wider than the row, the device
+    // copy keeps that pitch so that uploads are plain linear copies (a strided 2-D copy of
+    // 32 KB rows runs well below PCIe speed); the same for the output.
+    const bool lin_in = in_ld % 4 == 0 && in_ld - in_cols <= in_cols / 8;
+    const bool lin_out = out_ld == out_cols && out_cols % 4 == 0;   // never write host padding
+    const int64_t d_in_ld = lin_in ? in_ld : (in_cols + 3) / 4 * 4;
+    const int64_t d_out_ld = lin_out ? out_ld : (out_cols + 3) / 4 * 4;
     rc = stage_reserve(ctx, 0, (size_t)in_rows * d_in_ld * 4);
     if (rc) return rc;
     rc = stage_reserve(ctx, 1, (size_t)out_rows * d_out_ld * 4);
@@ -475,9 +481,16 @@ int gb200_blur3x3_f32_host(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
         if (r0 >= r1) break;
         const int64_t need = r1 + 2;
         if (need > uploaded) {
-            GB200_CUDA_TRY(cudaMemcpy2DAsync(d_in + uploaded * d_in_ld, d_in_ld * 4,
-                                             in + uploaded * in_ld, in_ld * 4, in_cols * 4,
-                                             need - uploaded, cudaMemcpyHostToDevice, up));
+            if (lin_in) {
+                // rows [uploaded, need) in one piece; the image's last row ends after in_cols
+                const int64_t elems = (need - uploaded - 1) * in_ld + (need == in_rows ? in_cols : in_ld);
+                GB200_CUDA_TRY(cudaMemcpyAsync(d_in + uploaded * d_in_ld, in + uploaded * in_ld,
+                                               elems * 4, cudaMemcpyHostToDevice, up));
+            } else {
+                GB200_CUDA_TRY(cudaMemcpy2DAsync(d_in + uploaded * d_in_ld, d_in_ld * 4,
+                                                 in + uploaded * in_ld, in_ld * 4, in_cols * 4,
+                                                 need - uploaded, cudaMemcpyHostToDevice, up));
+            }
             uploaded = need;
         }
         GB200_CUDA_TRY(cudaEventRecord(ctx->ev[0], up));
@@ -485,9 +498,15 @@ int gb200_blur3x3_f32_host(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
         rc = blur_dispatch(ctx, d_in + r0 * d_in_ld, d_in_ld, r1 - r0 + 2, in_cols,
                            d_out + r0 * d_out_ld, d_out_ld, down, 0);
         if (rc) return rc;
-        GB200_CUDA_TRY(cudaMemcpy2DAsync(out + r0 * out_ld, out_ld * 4, d_out + r0 * d_out_ld,
-                                         d_out_ld * 4, out_cols * 4, r1 - r0,
-                                         cudaMemcpyDeviceToHost, down));
+        if (lin_out) {
+            const int64_t elems = (r1 - r0 - 1) * out_ld + (r1 == out_rows ? out_cols : out_ld);
+            GB200_CUDA_TRY(cudaMemcpyAsync(out + r0 * out_ld, d_out + r0 * d_out_ld, elems * 4,
+                                           cudaMemcpyDeviceToHost, down));
+        } else {
+            GB200_CUDA_TRY(cudaMemcpy2DAsync(out + r0 * out_ld, out_ld * 4, d_out + r0 * d_out_ld,
+                                             d_out_ld * 4, out_cols * 4, r1 - r0,
+                                             cudaMemcpyDeviceToHost, down));
+        }
     }
     GB200_CUDA_TRY(cudaStreamSynchronize(up));
     GB200_CUDA_TRY(cudaStreamSynchronize(down));
