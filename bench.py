@@ -441,8 +441,10 @@ class GemmF32Workload(Workload):
     def units_per_step(self):
         return 2.0 * self.N ** 3
 
+    def pre_step(self):
+        self.flush.zero_()      # evict the 3 MB of operands from L2; outside the per-step events
+
     def step(self, stream):
-        self.flush.zero_()
         self.ctx.gemm_f32(self.a, self.a, self.c, stream=stream)
 
     def e2e_setup(self):
@@ -618,7 +620,10 @@ def main():
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         start.record()
+        pre = getattr(wl, "pre_step", None)
         for i in range(steps):
+            if pre is not None:
+                pre()
             evs[i][0].record()
             wl.step(stream)
             evs[i][1].record()
@@ -627,8 +632,9 @@ def main():
         clocks = sampler.stop() if rank == 0 else None
         ctx.sync()  # also surfaces a kernel that gave up a bounded wait
         launches = ctx.launch_count() - launches0
-        total_ms = start.elapsed_time(stop)
         per_launch_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+        # a workload that flushes L2 between steps is timed by its per-step events only
+        total_ms = per_launch_ms * steps if pre is not None else start.elapsed_time(stop)
         t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -30,7 +30,10 @@ constexpr int B_BYTES = BN * BK * 2;              // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int GROUP_M = 16;                       // tile rows per L2 rasterisation group
+#ifndef GB200_GEMM_GROUP_M
+#define GB200_GEMM_GROUP_M 16
+#endif
+constexpr int GROUP_M = GB200_GEMM_GROUP_M;       // tile rows per L2 rasterisation group
 }  // namespace gemm
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {

@@ -8,9 +8,10 @@
 // global memory after every K tile, bench.cu:41), each thread owns a TM x TN register tile
 // instead of one element, and edges are bounds-checked, so no divisibility is required.
 //
-// Every C element is accumulated by one thread in ascending k with fused multiply-adds, the
-// same order as the reference's CPU leaf (test/library/matrix/impl/cpu-matrix.h:196-212);
-// results differ from it only by fma-vs-(mul,add) rounding and K-tile reassociation.
+// Every C element is accumulated in ascending k with fused multiply-adds (one chain per K tile;
+// the small-problem kernel sums four K slices in a fixed order), the order of the reference's
+// tiled CPU path (test/library/matrix/impl/cpu-matrix.h:196-212 under Reduce(k_dim, tk)); results
+// differ from it only by fma-vs-(mul,add) rounding and K-tile reassociation.
 // fp32 inputs stay on the fp32 pipe on purpose: tf32 tensor cores would drop 13 mantissa bits.
 #include "common.cuh"
 
@@ -73,6 +74,111 @@ gemm_f32_kernel(const float *__restrict__ A, int64_t lda, const float *__restric
     }
 }
 
+// Kernel for problems too small to fill the machine with 128 x 128 tiles (the 512^3 correctness
+// configuration is one): a CTA owns a 32 x 32 tile of C and its four warps each reduce one
+// quarter of K on their own -- private shared-memory staging, no block barrier in the main loop,
+// the next 16 columns of K prefetched into registers while the current ones are multiplied -- and
+// the four partial tiles are summed through shared memory in a fixed order at the end, so the
+// result is deterministic.  Per lane: a 4 x 8 register tile, 3 shared loads per 32 FMAs.
+__global__ void __launch_bounds__(128)
+gemm_f32_warpk_kernel(const float *__restrict__ A, int64_t lda, const float *__restrict__ B,
+                      int64_t ldb, float *__restrict__ C, int64_t ldc, int M, int N, int K,
+                      int accumulate, int vec_ok) {
+    constexpr int BK = 16;
+    __shared__ __align__(16) float As[4][BK][32 + 4];   // [warp][k][m]
+    __shared__ __align__(16) float Bs[4][BK][32 + 4];   // [warp][k][n]
+    __shared__ __align__(16) float Cs[4][32][32 + 4];   // partial tiles
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    // this warp's slice of K, in whole BK chunks
+    const int chunks = (K + BK - 1) / BK;
+    const int per = (chunks + 3) / 4;
+    const int c_begin = warp * per, c_end = min(chunks, c_begin + per);
+    const int ty = lane >> 2, tx = lane & 3;   // 8 x 4 lanes: rows 4*ty.., cols 8*tx..
+    const bool interior = vec_ok && m0 + 32 <= M && n0 + 32 <= N;
+
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+    float4 pa[4], pb[4];   // prefetch registers: A row `lane`, 16 k; B row k = lane / 2, 16 n
+    auto fetch = [&](int c) {
+        const int k0 = c * BK;
+        if (interior && k0 + BK <= K) {
+            const float4 *ap = reinterpret_cast<const float4 *>(A + static_cast<int64_t>(m0 + lane) * lda + k0);
+            const float4 *bp = reinterpret_cast<const float4 *>(
+                B + static_cast<int64_t>(k0 + (lane >> 1)) * ldb + n0 + (lane & 1) * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                pa[q] = __ldg(ap + q);
+                pb[q] = __ldg(bp + q);
+            }
+        } else {
+            float ta[16], tb[16];
+            const int gm = m0 + lane, gk = k0 + (lane >> 1), gn = n0 + (lane & 1) * 16;
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+                ta[q] = (gm < M && k0 + q < K) ? A[static_cast<int64_t>(gm) * lda + k0 + q] : 0.0f;
+                tb[q] = (gk < K && gn + q < N) ? B[static_cast<int64_t>(gk) * ldb + gn + q] : 0.0f;
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                pa[q] = make_float4(ta[4 * q], ta[4 * q + 1], ta[4 * q + 2], ta[4 * q + 3]);
+                pb[q] = make_float4(tb[4 * q], tb[4 * q + 1], tb[4 * q + 2], tb[4 * q + 3]);
+            }
+        }
+    };
+    auto stage = [&]() {
+        // A arrives row-wise (lane = m): store transposed so that 4 consecutive m are one LDS.128
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            As[warp][4 * q + 0][lane] = pa[q].x;
+            As[warp][4 * q + 1][lane] = pa[q].y;
+            As[warp][4 * q + 2][lane] = pa[q].z;
+            As[warp][4 * q + 3][lane] = pa[q].w;
+            *reinterpret_cast<float4 *>(&Bs[warp][lane >> 1][(lane & 1) * 16 + 4 * q]) = pb[q];
+        }
+    };
+
+    if (c_begin < c_end) fetch(c_begin);
+    for (int c = c_begin; c < c_end; ++c) {
+        __syncwarp();   // everyone is done reading the previous chunk
+        stage();
+        __syncwarp();
+        if (c + 1 < c_end) fetch(c + 1);
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            const float4 a = *reinterpret_cast<const float4 *>(&As[warp][k][4 * ty]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[warp][k][8 * tx]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[warp][k][8 * tx + 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w};
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+    }
+    // partial tiles -> shared memory, then a fixed-order sum of the four K slices
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        *reinterpret_cast<float4 *>(&Cs[warp][4 * ty + i][8 * tx]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        *reinterpret_cast<float4 *>(&Cs[warp][4 * ty + i][8 * tx + 4]) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 32 * 32; e += 128) {
+        const int r = e >> 5, cidx = e & 31;
+        const int gm = m0 + r, gn = n0 + cidx;
+        if (gm < M && gn < N) {
+            const float sum = ((Cs[0][r][cidx] + Cs[1][r][cidx]) + Cs[2][r][cidx]) + Cs[3][r][cidx];
+            float *dst = C + static_cast<int64_t>(gm) * ldc + gn;
+            *dst = accumulate ? (*dst + sum) : sum;
+        }
+    }
+}
+
 int check_gemm_args(const void *A, int64_t lda, const void *B, int64_t ldb, void *C,
                            int64_t ldc, int64_t M, int64_t N, int64_t K, bool b_colmajor) {
     GB200_REQUIRE(M >= 0 && N >= 0 && K >= 0, GB200_ERR_INVALID_ARG, "negative extent");
@@ -97,8 +203,10 @@ int gemm_f32_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const float *
                                                                       (int)N, (int)K, accumulate);
     } else {
         dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32));
-        gemm_f32_kernel<32, 32, 32, 4, 4><<<grid, 64, 0, stream>>>(A, lda, B, ldb, C, ldc, (int)M,
-                                                                   (int)N, (int)K, accumulate);
+        const int vec_ok = (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+                           (reinterpret_cast<uintptr_t>(B) & 15) == 0 && lda % 4 == 0 && ldb % 4 == 0;
+        gemm_f32_warpk_kernel<<<grid, 128, 0, stream>>>(A, lda, B, ldb, C, ldc, (int)M, (int)N,
+                                                       (int)K, accumulate, vec_ok);
     }
     return after_launch(ctx, "gemm_f32_kernel");
 }
