@@ -318,7 +318,7 @@ class GemmBf16Workload(Workload):
     unit = "TFLOP/s"
     dtype = "bf16"
     bound = "tensor"
-    kernel = "gemm_bf16_tc_kernel"
+    kernel = "gemm_bf16_2cta_kernel"
     N = 8192
 
     def __init__(self, ctx, rank, world, torch, dist=None):

@@ -32,6 +32,7 @@ SIGNATURES = {
     "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
     "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
     "gb200_gemm_bf16_splitk": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
+    "gb200_gemm_bf16_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
     "gb200_gemm_bf16_splitk_static": None,
     "gb200_softmax_rows_f32": [_vp, _i64, _vp, _i64, _i64, _i64, _vp],
     "gb200_softmax_rows_f32_variant": [_vp, _i64, _vp, _i64, _i64, _i64, _vp, _int],
@@ -139,10 +140,15 @@ class Context:
         _check(lib.gb200_gemm_f32(self.handle, _ptr(A), _ld(A), _ptr(B), _ld(B), _ptr(C), _ld(C), M, N, K,
                                   int(bool(accumulate)), _stream(stream)), "gb200_gemm_f32")
 
-    def gemm_bf16(self, A, Bt, C, stream=None, splits=None):
+    def gemm_bf16(self, A, Bt, C, stream=None, splits=None, variant=None):
         """A: (M,K) bf16; Bt: (N,K) bf16 (column-major B); C: (M,N) bf16."""
         M, K = A.shape
         N = Bt.shape[0]
+        if variant is not None:
+            _check(lib.gb200_gemm_bf16_variant(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C),
+                                               _ld(C), M, N, K, _stream(stream), int(variant)),
+                   "gb200_gemm_bf16_variant")
+            return
         if splits is not None:
             _check(lib.gb200_gemm_bf16_splitk(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C),
                                               _ld(C), M, N, K, _stream(stream), int(splits)),

@@ -15,6 +15,8 @@
 //     tcgen05.commit;
 //   * warps 2-5 drain the finished accumulator with tcgen05.ld, round to bf16 and store C,
 //     overlapping the next tile's main loop (the other TMEM accumulator);
+//   * problems with at least one 256 x 256 tile per pair of SMs go to the CTA-pair kernel
+//     (gemm_bf16_2cta.cu, tcgen05.mma.cta_group::2), measured 3-4 % faster at 8192^3;
 //   * problems with too few tiles to fill the SMs are split along K: each (tile, split) item
 //     writes an fp32 partial slab to a workspace and a small second kernel sums the slabs.
 // Every wait is bounded; a wait that runs out records a code in the context's status word and
@@ -30,6 +32,9 @@ constexpr int B_BYTES = BN * BK * 2;              // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+#ifndef GB200_GEMM_AUTO_PAIR
+#define GB200_GEMM_AUTO_PAIR 1
+#endif
 #ifndef GB200_GEMM_GROUP_M
 #define GB200_GEMM_GROUP_M 16
 #endif
@@ -289,9 +294,13 @@ int pick_splits(int64_t n_tiles, int64_t k_blocks, int sm_count) {
     return s < 2 ? 1 : (int)s;
 }
 
+int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream);
+
+// kernel_choice: 0 = pick, 1 = single-CTA tiles, 2 = CTA-pair tiles.
 int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                        void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream,
-                       int forced_splits = 0) {
+                       int forced_splits = 0, int kernel_choice = 0) {
     using namespace gemm;
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     const bool tc_ok = ctx->encode_tiled && al16(A) && al16(B) && lda % 8 == 0 && ldb % 8 == 0 &&
@@ -312,6 +321,12 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     if (rc) return rc;
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int splits = forced_splits > 0 ? forced_splits : pick_splits(n_tiles, (K + BK - 1) / BK, ctx->sm_count);
+    // CTA-pair tiles (256 x 256) when there are enough of them to fill the SM pairs
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const bool want_pair = kernel_choice == 2 ||
+                           (kernel_choice == 0 && GB200_GEMM_AUTO_PAIR && pair_tiles >= ctx->sm_count / 2);
+    if (want_pair && splits == 1 && forced_splits <= 1)
+        return gemm_bf16_2cta_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, stream);
     float *ws = nullptr;
     if (splits > 1) {
         rc = workspace_reserve(ctx, (size_t)splits * M * N * sizeof(float));
@@ -487,6 +502,18 @@ int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int
         GB200_REQUIRE(err == cudaSuccess, GB200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(err));
     }
     return GB200_OK;
+}
+
+// Test / benchmark hook: kernel chosen by the caller (1 = single-CTA tiles, 2 = CTA-pair tiles).
+int gb200_gemm_bf16_variant(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                            void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream,
+                            int variant) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return gemm_bf16_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K,
+                              static_cast<cudaStream_t>(stream), 1, variant);
 }
 
 int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,

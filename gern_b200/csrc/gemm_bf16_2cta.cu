@@ -1,0 +1,285 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256 x 256 tile of C per pair of SMs.
+//
+// Same operator and operand layout as gemm_bf16_tc_kernel (gemm_bf16.cu); what changes is the
+// mapping onto the machine.  Two CTAs of a cluster share one MMA: CTA r of the pair holds rows
+// [128 r, 128 r + 128) of the A tile and columns [128 r, 128 r + 128) of the B tile in its shared
+// memory, the leader (rank 0) issues M256 N256 K16 instructions that read both CTAs' operand
+// halves, and each CTA's TMEM receives the accumulator rows of its own half of M.  Per CTA and
+// MMA that is 4 KiB of A + 4 KiB of B from shared memory instead of 4 + 8 for the 128 x 256
+// single-CTA tile, and each B tile is fetched from L2 once per pair, which leaves room for a
+// 6-deep ring.  Every CTA loads its own halves with ordinary (non-multicast) TMA tile loads that
+// report their bytes to the leader's barrier; ring slots and accumulators are released to both
+// CTAs with tcgen05.commit on both CTAs' barriers.  Waits on mbarriers are time-bounded; the
+// cluster barriers at start and end are the only unbounded synchronisation and are reached by
+// every thread on every path.
+#include "common.cuh"
+
+namespace gb200 {
+
+#ifndef GB200_GEMM2_STAGES
+#define GB200_GEMM2_STAGES 6
+#endif
+#ifndef GB200_GEMM2_GROUP_M
+#define GB200_GEMM2_GROUP_M 8
+#endif
+
+namespace gemm2 {
+constexpr int BM = 256, BN = 256, BK = 64, STAGES = GB200_GEMM2_STAGES;
+constexpr int HALF = 128;                            // rows of A / of B per CTA
+constexpr int A_BYTES = HALF * BK * 2;               // 16 KiB
+constexpr int B_BYTES = HALF * BK * 2;               // 16 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 32 KiB per CTA
+constexpr int NUM_THREADS = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GROUP_M = GB200_GEMM2_GROUP_M;         // 256-row tile rows per rasterisation group
+}  // namespace gemm2
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+// TMA tile load of this CTA's operand half; the byte count is reported to the barrier at
+// cluster address `bar_cluster_addr` (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *tmap, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this shared-memory offset in both CTAs of the pair, once every
+// MMA issued so far has completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
+            "r"(smem_u32(bar)),
+        "h"(mask)
+        : "memory");
+}
+
+__device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
+    const int per_group = gemm2::GROUP_M * tiles_n;
+    const int g = t / per_group;
+    const int first_m = g * gemm2::GROUP_M;
+    const int rows_in_group = min(gemm2::GROUP_M, tiles_m - first_m);
+    const int r = t - g * per_group;
+    tm = first_m + r % rows_in_group;
+    tn = r / rows_in_group;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::NUM_THREADS, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
+                      int64_t ldc, int M, int N, int K, int *status) {
+    using namespace gemm2;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
+    uint64_t *full = bars;                        // [STAGES] used in the leader only
+    uint64_t *empty = bars + STAGES;              // [STAGES] one per CTA
+    uint64_t *acc_full = bars + 2 * STAGES;       // [2] one per CTA
+    uint64_t *acc_empty = bars + 2 * STAGES + 2;  // [2] used in the leader only (8 arrivals)
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int n_tiles = tiles_m * tiles_n;
+    const int k_blocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 8);   // 4 epilogue warps in each of the two CTAs
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_base_slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+                int tm, tn;
+                tile_coords2(t, tiles_m, tiles_n, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty[s], ph ^ 1, status, 221)) { ok = false; break; }
+                    unsigned char *sa = smem + s * STAGE_BYTES;
+                    // the leader's barrier collects the bytes of all four loads of the pair
+                    if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                    const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
+                    tma_load_2d_pair(sa, &tmap_a, kb * BK, tm * BM + (int)rank * HALF, full_leader);
+                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, kb * BK, tn * BN + (int)rank * HALF, full_leader);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0);
+            uint32_t it = 0, tile_it = 0;
+            bool ok = true;
+            for (int t = pair; t < n_tiles && ok; t += n_pairs, ++tile_it) {
+                const int buf = tile_it & 1;
+                const uint32_t acc_ph = (tile_it >> 1) & 1;
+                if (!mbar_wait(&acc_empty[buf], acc_ph ^ 1, status, 222)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[s], ph, status, 223)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                    const uint64_t da = umma_desc_sw128(sa, 16, 1024);
+                    const uint64_t db = umma_desc_sw128(sa + A_BYTES, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_f16_ss_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc,
+                                         (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(&empty[s]);   // frees the slot in both CTAs
+                }
+                if (ok) umma_commit_pair(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): TMEM -> registers -> bf16 -> global ----------------
+        const int lane_group = warp & 3;
+        uint32_t tile_it = 0;
+        bool ok = true;
+        const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        for (int t = pair; t < n_tiles && ok; t += n_pairs, ++tile_it) {
+            int tm, tn;
+            tile_coords2(t, tiles_m, tiles_n, tm, tn);
+            const int buf = tile_it & 1;
+            const uint32_t acc_ph = (tile_it >> 1) & 1;
+            if (!mbar_wait(&acc_full[buf], acc_ph, status, 224)) { ok = false; break; }
+            tc_fence_after();
+            const int row = tm * BM + (int)rank * HALF + lane_group * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                                   static_cast<uint32_t>(buf * BN);
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + ch * 32, r);
+                tmem_ld_wait();
+                const int col = tn * BN + ch * 32;
+                if (row < M && col < N) {
+                    __nv_bfloat16 *dst = C + static_cast<int64_t>(row) * ldc + col;
+                    if (vec_ok && col + 32 <= N) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 v;
+                            v.x = pack_bf16(__uint_as_float(r[8 * q + 0]), __uint_as_float(r[8 * q + 1]));
+                            v.y = pack_bf16(__uint_as_float(r[8 * q + 2]), __uint_as_float(r[8 * q + 3]));
+                            v.z = pack_bf16(__uint_as_float(r[8 * q + 4]), __uint_as_float(r[8 * q + 5]));
+                            v.w = pack_bf16(__uint_as_float(r[8 * q + 6]), __uint_as_float(r[8 * q + 7]));
+                            *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < N) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            // the accumulator buffer is free once both CTAs have drained their halves
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // no CTA may leave while its partner can still signal into it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+// Launches the pair kernel; the caller has checked alignment (same rules as the single-CTA path).
+int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    using namespace gemm2;
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
+                         (uint64_t)lda * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
+                     (uint64_t)ldb * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int64_t pairs = ctx->sm_count / 2;
+    if (pairs > n_tiles) pairs = n_tiles;
+    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_2cta_kernel,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_bf16_2cta_kernel<<<(unsigned)(2 * pairs), NUM_THREADS, SMEM_BYTES, stream>>>(
+        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, ctx->d_status);
+    return after_launch(ctx, "gemm_bf16_2cta_kernel");
+}
+
+}  // namespace gb200

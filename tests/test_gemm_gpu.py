@@ -120,6 +120,35 @@ def test_bf16_split_k(ctx, oracle, mnk, splits):
     assert torch.equal(c, c2)
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("mnk", [(256, 256, 64), (512, 768, 1024), (300, 500, 200), (130, 258, 136), (1, 8, 8),
+                                 (1024, 1280, 512)])
+def test_bf16_kernel_variants(ctx, oracle, mnk, variant):
+    """Single-CTA 128x256 tiles (1) and CTA-pair 256x256 tiles (2), forced, ragged shapes included."""
+    m, n, k = mnk
+    g = torch.Generator(device="cuda").manual_seed(m * 3 + n * 5 + k)
+    a = (torch.randn((m, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    c = torch.full((m, n + 8), 9.0, dtype=torch.bfloat16, device="cuda")
+    ctx.gemm_bf16(a, b, c[:, :n], variant=variant)
+    ctx.sync()
+    assert bool((c[:, n:] == 9.0).all()), "wrote past the row"
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.gemm_bf16(np.ascontiguousarray(bits(a)), np.ascontiguousarray(bits(b)))
+    oracle.set_threads(1)
+    assert frob(c[:, :n].float().cpu().numpy(), want) <= 3e-3
+
+
+def test_bf16_pair_kernel_exact_on_integers(ctx):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randint(-3, 4, (2048, 1024), device="cuda", generator=g).to(torch.bfloat16)
+    b = torch.randint(-3, 4, (1536, 1024), device="cuda", generator=g).to(torch.bfloat16)
+    c = torch.empty((2048, 1536), dtype=torch.bfloat16, device="cuda")
+    ctx.gemm_bf16(a, b, c, variant=2)
+    ctx.sync()
+    assert torch.equal(c, (a.float() @ b.float().T).to(torch.bfloat16))
+
+
 def test_bf16_unaligned_falls_to_simple_kernel(ctx, oracle):
     a, b, c = run_bf16(ctx, 70, 90, 50, seed=1, pad=3)   # pitch not a multiple of 8 elements
     want = oracle.gemm_bf16(np.ascontiguousarray(bits(a.contiguous())), np.ascontiguousarray(bits(b.contiguous())))
