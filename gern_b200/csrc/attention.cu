@@ -408,13 +408,24 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
 }
 
+int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
+                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
+                          int64_t d, float scale, cudaStream_t stream);
+
+#ifndef GB200_ATTN_AUTO_PAIR
+#define GB200_ATTN_AUTO_PAIR 0
+#endif
+
+// kernel_choice: 0 = pick, 1 = one CTA per two Q tiles, 2 = CTA pairs (attention_pair.cu).
 int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                        const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
-                       int64_t d, float scale, cudaStream_t stream) {
+                       int64_t d, float scale, cudaStream_t stream, int kernel_choice = 0) {
     using namespace attn;
     GB200_REQUIRE(d == D, GB200_ERR_UNSUPPORTED, "attention: d must be %d in this build (got %lld)",
                   D, (long long)d);
     GB200_REQUIRE(ctx->encode_tiled != nullptr, GB200_ERR_NO_DEVICE, "TMA descriptors unavailable");
+    if (kernel_choice == 2 || (kernel_choice == 0 && GB200_ATTN_AUTO_PAIR))
+        return attention_pair_launch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale, stream);
     CUtensorMap tq, tk, tv;
     int rc = get_tmap_2d(ctx, Q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)d, (uint64_t)nq,
                          (uint64_t)ldq * 2, 64, BM, CU_TENSOR_MAP_SWIZZLE_128B, &tq);
@@ -470,6 +481,19 @@ int gb200_attn_trace_read(long long *out) {
     return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 16 * 64);
 }
 #endif
+
+// Test / benchmark hook: kernel chosen by the caller (1 = single CTA, 2 = CTA pair).
+int gb200_attention_bf16_variant(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K,
+                                 int64_t ldk, const void *V, int64_t ldv, void *O, int64_t ldo,
+                                 int64_t nq, int64_t nkv, int64_t d, float scale, void *stream,
+                                 int variant) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
+                              static_cast<cudaStream_t>(stream), variant);
+}
 
 int gb200_attention_bf16_host(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K,
                               int64_t ldk, const void *V, int64_t ldv, void *O, int64_t ldo,

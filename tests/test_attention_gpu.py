@@ -36,6 +36,33 @@ def test_against_oracle(ctx, oracle, nq, nkv):
     assert frob(o.float().cpu().numpy(), want) <= 1e-2
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("nq,nkv", [(256, 128), (256, 1024), (100, 200), (130, 129), (1, 1), (640, 2048)])
+def test_kernel_variants(ctx, oracle, nq, nkv, variant):
+    """Single-CTA two-tile kernel (1) and CTA-pair kernel (2), forced."""
+    q, k, v = make(nq, nkv, nq * 7 + nkv)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / np.sqrt(128.0)
+    ctx.attention_bf16(q, k, v, o, scale, variant=variant)
+    ctx.sync()
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), scale)
+    oracle.set_threads(1)
+    assert frob(o.float().cpu().numpy(), want) <= 1e-2
+
+
+def test_pair_kernel_rescale_path(ctx, oracle):
+    nq, nkv = 256, 1024
+    q, k, v = make(nq, nkv, 5, std=1.0)
+    ramp = torch.linspace(0.2, 3.0, nkv, device="cuda").unsqueeze(1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    ctx.attention_bf16(q, k, v, o, 1.0, variant=2)
+    ctx.sync()
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), 1.0)
+    assert frob(o.float().cpu().numpy(), want) <= 1e-2
+
+
 def test_peaked_rows_exercise_the_rescale(ctx, oracle):
     """Large logits whose maximum keeps growing along kv force the running-max correction."""
     nq, nkv = 128, 1024
