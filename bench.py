@@ -428,7 +428,7 @@ class GemmF32Workload(Workload):
     unit = "TFLOP/s"
     dtype = "f32"
     bound = "tensor"
-    kernel = "gemm_f32_kernel"
+    kernel = "gemm_f32_warpk_kernel"
     N = 512
 
     def __init__(self, ctx, rank, world, torch, dist=None):
