@@ -60,6 +60,24 @@ lib.gb200_launch_count.argtypes = [_vp]
 lib.gb200_launch_count.restype = _i64
 lib.gb200_gemm_bf16_splitk_static.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]
 lib.gb200_gemm_bf16_splitk_static.restype = _int
+
+
+class Shard(ctypes.Structure):
+    """gb200_shard: one device's rows of a sharded call."""
+    _fields_ = [("ctx", _vp), ("in_", _vp), ("out", _vp), ("rows", _i64), ("shared0", _vp),
+                ("shared1", _vp), ("stream", _vp)]
+
+
+_shards_p = ctypes.POINTER(Shard)
+lib.gb200_gemm_bf16_sharded.argtypes = [_shards_p, _int, _i64, _i64, _i64, _i64, _i64]
+lib.gb200_softmax_rows_f32_sharded.argtypes = [_shards_p, _int, _i64, _i64, _i64]
+lib.gb200_attention_bf16_sharded.argtypes = [_shards_p, _int, _i64, _i64, _i64, _i64, _i64, _i64,
+                                             ctypes.c_float]
+lib.gb200_blur3x3_f32_sharded.argtypes = [_shards_p, _int, _i64, _i64, _i64]
+for _name in ("gb200_gemm_bf16_sharded", "gb200_softmax_rows_f32_sharded",
+              "gb200_attention_bf16_sharded", "gb200_blur3x3_f32_sharded"):
+    SIGNATURES[_name] = None
+    getattr(lib, _name).restype = _int
 for _name, _args in SIGNATURES.items():
     if _args is not None and hasattr(lib, _name):
         getattr(lib, _name).argtypes = [_vp] + _args
@@ -107,6 +125,47 @@ def gemm_bf16_splitk_static(A, Bt, C, splits=0, stream=None):
     N = Bt.shape[0]
     _check(lib.gb200_gemm_bf16_splitk_static(_ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N, K,
                                              int(splits), _stream(stream)), "gb200_gemm_bf16_splitk_static")
+
+
+def _shard_array(parts):
+    """parts: list of (Context, in, out, shared0, shared1, stream); rows come from `in`."""
+    arr = (Shard * len(parts))()
+    for g, (ctx, x, out, s0, s1, stream) in enumerate(parts):
+        arr[g] = Shard(ctx.handle, _ptr(x), _ptr(out), x.shape[0], _ptr(s0), _ptr(s1), _stream(stream))
+    return arr
+
+
+def gemm_bf16_sharded(parts):
+    """parts: one (Context, A_panel, C_panel, Bt_replica) per device."""
+    a0, c0, b0 = parts[0][1], parts[0][2], parts[0][3]
+    arr = _shard_array([(c, a, o, b, None, None) for c, a, o, b in parts])
+    _check(lib.gb200_gemm_bf16_sharded(arr, len(parts), _ld(a0), _ld(b0), _ld(c0), b0.shape[0],
+                                       a0.shape[1]), "gb200_gemm_bf16_sharded")
+
+
+def softmax_rows_sharded(parts):
+    """parts: one (Context, x_rows, out_rows) per device."""
+    x0, o0 = parts[0][1], parts[0][2]
+    arr = _shard_array([(c, x, o, None, None, None) for c, x, o in parts])
+    _check(lib.gb200_softmax_rows_f32_sharded(arr, len(parts), _ld(x0), _ld(o0), x0.shape[1]),
+           "gb200_softmax_rows_f32_sharded")
+
+
+def attention_bf16_sharded(parts, scale):
+    """parts: one (Context, Q_rows, O_rows, K_replica, V_replica) per device."""
+    q0, o0, k0, v0 = parts[0][1], parts[0][2], parts[0][3], parts[0][4]
+    arr = _shard_array([(c, q, o, k, v, None) for c, q, o, k, v in parts])
+    _check(lib.gb200_attention_bf16_sharded(arr, len(parts), _ld(q0), _ld(k0), _ld(v0), _ld(o0),
+                                            k0.shape[0], q0.shape[1], ctypes.c_float(scale)),
+           "gb200_attention_bf16_sharded")
+
+
+def blur3x3_sharded(parts):
+    """parts: one (Context, band, out_band) per device, bands in image order."""
+    x0, o0 = parts[0][1], parts[0][2]
+    arr = _shard_array([(c, x, o, None, None, None) for c, x, o in parts])
+    _check(lib.gb200_blur3x3_f32_sharded(arr, len(parts), _ld(x0), x0.shape[1], _ld(o0)),
+           "gb200_blur3x3_f32_sharded")
 
 
 class Context:

@@ -134,6 +134,40 @@ int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void 
                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                          int64_t nkv, int64_t d, float scale, void *stream);
 
+/* ---- single-process multi-GPU forms ---------------------------------------------------- */
+
+/* One device's part of a row-sharded call.  The reference launches on device 0 only
+ * (src/codegen/codegen.cpp:576-611 emits no device selection) and has nothing like it. */
+typedef struct gb200_shard {
+    gb200_ctx *ctx;      /* context of the device that holds this shard's memory              */
+    const void *in;      /* this shard's rows of the sharded input (A panel, softmax rows,    */
+                         /* Q rows, image band)                                               */
+    void *out;           /* this shard's rows of the result                                   */
+    int64_t rows;        /* rows in this shard (0 = the device sits this call out)            */
+    const void *shared0; /* this device's replica of the unsharded operand: B, or K           */
+    const void *shared1; /* second replicated operand: V (attention only)                     */
+    void *stream;        /* cudaStream_t on ctx's device; NULL = legacy default stream        */
+} gb200_shard;
+
+/* Each call enqueues shard g on shards[g].ctx's device and stream and returns without
+ * synchronising; the calling thread's current device is restored.  Operand conventions are those
+ * of the single-device entry point of the same name.  GEMM shards the M rows of A and C (B
+ * replicated per device), softmax shards rows, attention shards the rows of Q and O (K, V
+ * replicated): no data crosses devices.  The fp32 matmul has no sharded form (replicas only). */
+int gb200_gemm_bf16_sharded(const gb200_shard *shards, int n, int64_t lda, int64_t ldb,
+                            int64_t ldc, int64_t N, int64_t K);
+int gb200_softmax_rows_f32_sharded(const gb200_shard *shards, int n, int64_t ld_in,
+                                   int64_t ld_out, int64_t cols);
+int gb200_attention_bf16_sharded(const gb200_shard *shards, int n, int64_t ldq, int64_t ldk,
+                                 int64_t ldv, int64_t ldo, int64_t nkv, int64_t d, float scale);
+/* Blur over an image cut into n consecutive row bands: shards[g].in holds shards[g].rows input
+ * rows (>= 2) and shards[g].out receives as many output rows, except the last band, which
+ * receives rows - 2.  Band g's kernel reads the first two rows of band g+1 directly from the
+ * memory of the device that holds it (peer access is enabled on first use; ordinary loads over
+ * NVLink, no copy, no extra launch). */
+int gb200_blur3x3_f32_sharded(const gb200_shard *shards, int n, int64_t in_ld, int64_t in_cols,
+                              int64_t out_ld);
+
 /* ---- host-buffer forms (operands and results in host memory) -------------------------- */
 
 int gb200_gemm_f32_host(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
