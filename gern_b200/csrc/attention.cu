@@ -5,20 +5,21 @@
 // mm(P,V -> O) )  with S and P as per-tile temporaries, the shape of the reference's chained
 // matmul fusion (test/test-cpu-mm.cpp:266-408, E = (A*B)*D with C allocated per tile) with the
 // five softmax ops (apps/common/annot/functions.h:9-173) between the two multiplies.  Here the
-// temporaries never reach HBM: S lives in TMEM, P is re-quantised to bf16 into shared memory as
-// the A operand of the second multiply, and the softmax is computed online over 128-wide blocks
+// temporaries never reach HBM: S lives in TMEM, P is re-quantised to bf16 in place (over the first
+// half of S's columns) and read from TMEM as the A operand of the second multiply, and the softmax is computed online over 128-wide blocks
 // of K/V with a running row maximum and row sum.
 //
-// One CTA owns two 128-row tiles of Q.  Warp 9 streams K and V blocks through one 3-slot TMA
+// One CTA owns two 128-row tiles of Q.  Warp 9 streams K and V blocks through one 5-slot TMA
 // ring (K_0 V_0 K_1 V_1 ...); warp 8 issues tcgen05.mma in the order P_t V_j, Q_t K_{j+1}^T for
 // tile t = 0, 1, so that while one tile's S is in the softmax the tensor pipe works on the other
 // tile; warps 0-3 (tile 0) and 4-7 (tile 1) own one row each: they read S_t from TMEM with all
-// loads in flight at once (a TMEM round trip costs a few hundred cycles), update max/sum, write P_t to shared
-// memory in the 128-byte-swizzled K-major layout the MMA reads, rescale O_t in TMEM when the
-// running maximum has grown by more than 2^8, and at the end normalise and store O.  P is packed
-// to bf16 with integer adds and a byte permute, because the conversion instruction shares the
-// 16-lane unit the exponentials keep busy.  Every wait is bounded and reports
-// through the status word.
+// loads in flight at once (a TMEM round trip costs a few hundred cycles), update max/sum, write P_t back
+// to TMEM (two bf16 per column, so that the second multiply reads only V from shared memory: with
+// both operands in shared memory a 128 x 128 x 16 MMA needs the full 128 bytes per clock of the
+// shared-memory port and the softmax's own stores starve it), rescale O_t in TMEM when the
+// running maximum has grown by more than 2^8, and at the end normalise and store O.  The first half of P_t (kv 0-63) is announced to the
+// MMA warp while the second half is still being computed, so that half of P_t V_j runs under the
+// softmax.  Every wait is bounded and reports through the status word.
 #include <float.h>
 
 #include <type_traits>
@@ -32,11 +33,12 @@ constexpr int BM = 128, BN = 128, D = 128;
 constexpr int TILES = 2;                   // Q tiles (of BM rows) per CTA
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: any 128 x 128 bf16 tile (2 swizzle chunks)
 constexpr int CHUNK_BYTES = 128 * 128;     // 16 KiB: 128 rows x 64 bf16
-constexpr int KV_SLOTS = 3;                // one ring for K_0 V_0 K_1 V_1 ...
+constexpr int KV_SLOTS = 5;                // one ring for K_0 V_0 K_1 V_1 ...
 constexpr int NUM_THREADS = 320;           // 8 softmax warps + MMA warp + TMA warp
-// Q (2 tiles), P (2 tiles), K/V ring, then barriers
-constexpr int SMEM_BYTES = (2 * TILES + KV_SLOTS) * TILE_BYTES + 1024 + 256;
-constexpr uint32_t TMEM_COLS = 512;        // S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512)
+// Q (2 tiles), K/V ring, then barriers
+constexpr int SMEM_BYTES = (TILES + KV_SLOTS) * TILE_BYTES + 1024 + 256;
+// S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t (bf16 pairs) overwrites S_t's first 64
+constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 }  // namespace attn
 
@@ -46,6 +48,12 @@ constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 // keeps every exponential on the MUFU; the cubic stays available for shapes where it pays.
 #ifndef GB200_POLY_AND
 #define GB200_POLY_AND 255
+#endif
+#ifndef GB200_ATTN_PACK_CVT
+#define GB200_ATTN_PACK_CVT 1
+#endif
+#ifndef GB200_ATTN_MAX3
+#define GB200_ATTN_MAX3 1
 #endif
 
 #ifdef GB200_ATTN_TRACE
@@ -90,10 +98,17 @@ __device__ __forceinline__ uint64_t poly_exp2_pair(uint64_t x2) {
     return pk2(p0, p1);
 }
 // Two non-negative finite fp32 values -> two bf16 (round half up) in one word, on the integer
-// pipe.  The F2FP conversion instruction shares the 16-lane-per-clock unit with the MUFU, which
-// the exponentials already saturate; two integer adds and a byte permute do not.
+// pipe (two adds and a byte permute instead of one cvt.rn.bf16x2.f32).  With P in shared memory
+// this was the faster form; with P in TMEM the conversion instruction measures 4 % faster
+// (71.0 -> 68.0 us at 32768 x 4096 x 128) and is the default (GB200_ATTN_PACK_CVT).
 __device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
     return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
+// max(a, b, c) in one instruction (three-input form of max.f32, sm_100 and later).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 __device__ __forceinline__ uint64_t mufu_exp2_pair(uint64_t x2) {
     float x0, x1;
@@ -111,16 +126,16 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char *sQ = smem;                               // [TILES] tiles
-    unsigned char *sP = smem + TILES * TILE_BYTES;          // [TILES] tiles
-    unsigned char *sKV = smem + 2 * TILES * TILE_BYTES;     // [KV_SLOTS] tiles
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (2 * TILES + KV_SLOTS) * TILE_BYTES);
-    uint64_t *q_full = bars;            // [1]
-    uint64_t *kv_full = bars + 1;       // [3]
-    uint64_t *kv_empty = bars + 4;      // [3]
-    uint64_t *s_full = bars + 7;        // [2] MMA -> softmax t: S_t holds block j
-    uint64_t *sp_ready = bars + 9;      // [2] softmax t -> MMA: P_t written, S_t consumed
-    uint64_t *o_full = bars + 11;       // [2] MMA -> softmax t: O_t final
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 13);
+    unsigned char *sKV = smem + TILES * TILE_BYTES;         // [KV_SLOTS] tiles
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (TILES + KV_SLOTS) * TILE_BYTES);
+    uint64_t *q_full = bars;                      // [1]
+    uint64_t *kv_full = bars + 1;                 // [KV_SLOTS]
+    uint64_t *kv_empty = kv_full + KV_SLOTS;      // [KV_SLOTS]
+    uint64_t *s_full = kv_empty + KV_SLOTS;       // [2] MMA -> softmax t: S_t holds block j
+    uint64_t *sp_ready = s_full + TILES;          // [2] softmax t -> MMA: P_t written over S_t
+    uint64_t *o_full = sp_ready + TILES;          // [2] MMA -> softmax t: O_t final
+    uint64_t *p_half = o_full + TILES;            // [2] softmax t -> MMA: kv 0-63 of P_t written
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(p_half + TILES);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * (BM * TILES);
@@ -139,6 +154,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             mbar_init(&s_full[t], 1);
             mbar_init(&sp_ready[t], 4);
             mbar_init(&o_full[t], 1);
+            mbar_init(&p_half[t], 4);
         }
         mbar_fence_init();
     }
@@ -192,17 +208,15 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
                 umma_commit(&s_full[t]);
             };
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t p_addr = smem_u32(sP + t * TILE_BYTES);
+            auto issue_pv = [&](int t, int j, int half) {
                 const uint32_t v_addr = smem_u32(sKV + ((2 * j + 1) % KV_SLOTS) * TILE_BYTES);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks) {
-                    // A = P: K-major, 16 kv values = 32 bytes inside the swizzle row.
-                    const uint32_t a_off = (ks / 4) * CHUNK_BYTES + (ks % 4) * 32;
+                for (int ks = half * 4; ks < half * 4 + 4; ++ks) {
+                    // A = P from TMEM: row = lane, 16 kv values = 8 columns of bf16 pairs.
                     // B = V: MN-major; 16 kv rows = 2048 bytes; the two 64-wide d chunks are
                     // CHUNK_BYTES apart (leading offset), 8-row groups 1024 bytes apart.
                     const uint32_t b_off = ks * 16 * 128;
-                    umma_f16_ss(tmem_base + 256 + t * D, umma_desc_sw128(p_addr + a_off, 16, 1024),
+                    umma_f16_ts(tmem_base + 256 + t * D, tmem_base + t * BN + ks * 8,
                                 umma_desc_sw128(v_addr + b_off, CHUNK_BYTES, 1024), idesc_pv,
                                 (j | ks) != 0);
                 }
@@ -220,10 +234,15 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const bool more = j + 1 < n_blocks;
                 if (more && !wait_kv(2 * j + 2)) { ok = false; break; }
                 for (int t = 0; t < TILES; ++t) {
+                    // the first half of P_t (kv 0-63) is announced while the softmax still works
+                    // on the second, so half of P_t V_j leaves the chain softmax -> PV -> QK
+                    if (!mbar_wait(&p_half[t], j & 1, status, 306)) { ok = false; break; }
+                    tc_fence_after();
+                    issue_pv(t, j, 0);
                     if (!mbar_wait(&sp_ready[t], j & 1, status, 307)) { ok = false; break; }
                     ATTN_TRACE(8 + 2 * t, j);
                     tc_fence_after();
-                    issue_pv(t, j);
+                    issue_pv(t, j, 1);
                     if (more)
                         issue_qk(t, j + 1);   // completes after PV(t, j): tensor pipe is in order
                     else
@@ -247,8 +266,6 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         float m_used = -FLT_MAX;  // maximum the exponentials are taken against (log2 domain)
         float l = 0.0f;           // running row sum
         bool ok = true;
-        unsigned char *p_row = sP + t * TILE_BYTES + row_in_tile * 128;
-        const int sw = row_in_tile & 7;
 
         for (int j = 0; j < n_blocks && ok; ++j) {
             // s_full(j) also tells that P_t V_{j-1} has finished: the tensor pipe runs in order.
@@ -272,8 +289,13 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
+#if GB200_ATTN_MAX3
+                        m0 = max3(m0, __uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1]));
+                        m1 = max3(m1, __uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3]));
+#else
                         m0 = fmaxf(m0, fmaxf(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])));
                         m1 = fmaxf(m1, fmaxf(__uint_as_float(sr[c][i + 2]), __uint_as_float(sr[c][i + 3])));
+#endif
                     }
                 m_blk = fmaxf(m0, m1);
             } else {
@@ -316,10 +338,8 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const uint64_t scale2 = pk2(scale_log2, scale_log2);
             const uint64_t negm2 = pk2(-m_used, -m_used);
 
-            // pass 2: p = 2^(s * scale_log2 - m) on fp32x2 pairs (even pairs on the MUFU, odd pairs
-            // as a cubic on the FMA pipe), row sum, and bf16 P into shared memory in the 128-byte
-            // swizzled K-major layout (16-byte unit u of row r sits at unit u ^ (r % 8)); kv 0-63
-            // go to the first 64-column chunk of the tile, 64-127 to the second.
+            // pass 2: p = 2^(s * scale_log2 - m) on fp32x2 pairs, row sum, and bf16 P back into
+            // TMEM, two kv values per 32-bit column (the lower kv index in the low half).
             uint64_t sum2 = pk2(0.0f, 0.0f);
             auto exp_chunk = [&](auto masked, int c, const uint32_t(&sr)[32]) {
                 uint32_t pb[16];
@@ -336,14 +356,22 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                         e2 = pk2(e0, e1);
                     }
                     sum2 = add2(sum2, e2);
+#if GB200_ATTN_PACK_CVT
+                    pb[k] = pack_bf16(e0, e1);
+#else
                     pb[k] = pack_bf16_alu(e0, e1);
+#endif
                 }
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int unit = (c & 1) * 4 + q;
-                    *reinterpret_cast<uint4 *>(p_row + (c >> 1) * CHUNK_BYTES + ((unit ^ sw) << 4)) =
-                        make_uint4(pb[4 * q], pb[4 * q + 1], pb[4 * q + 2], pb[4 * q + 3]);
+                if (c == 2) {
+                    // chunks 0 and 1 were stored a whole chunk ago: this wait does not stall
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_half[t]);
                 }
+                // P chunk c lands on columns [16c, 16c+16) of S_t, which chunk c's own load (columns
+                // [32c, 32c+32)) and every earlier one have already left.
+                tmem_st_32x16(t_s + c * 16, pb);
             };
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -359,7 +387,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const float sum = sum_lo + sum_hi;
             l += sum;
             if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 2, j);
-            fence_proxy_async_smem();
+            tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sp_ready[t]);
