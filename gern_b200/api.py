@@ -62,6 +62,18 @@ lib.gb200_gemm_bf16_splitk_static.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _
 lib.gb200_gemm_bf16_splitk_static.restype = _int
 
 
+class GemmEpilogue(ctypes.Structure):
+    """gb200_gemm_epilogue."""
+    _fields_ = [("alpha", ctypes.c_float), ("row_sub", _vp), ("apply_exp", _int), ("row_div", _vp),
+                ("row_max", _vp), ("row_sum", _vp)]
+
+
+lib.gb200_gemm_bf16_epilogue.argtypes = [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
+                                         ctypes.POINTER(GemmEpilogue), _vp]
+lib.gb200_gemm_bf16_epilogue.restype = _int
+SIGNATURES["gb200_gemm_bf16_epilogue"] = None
+
+
 class Shard(ctypes.Structure):
     """gb200_shard: one device's rows of a sharded call."""
     _fields_ = [("ctx", _vp), ("in_", _vp), ("out", _vp), ("rows", _i64), ("shared0", _vp),
@@ -217,6 +229,17 @@ class Context:
             return
         _check(lib.gb200_gemm_bf16(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N,
                                    K, _stream(stream)), "gb200_gemm_bf16")
+
+    def gemm_bf16_epilogue(self, A, Bt, C=None, alpha=1.0, row_sub=None, apply_exp=False, row_div=None,
+                           row_max=None, row_sum=None, stream=None):
+        """C = bf16(epilogue(alpha * A Bt^T)); any of C / row_max / row_sum may be left out."""
+        M, K = A.shape
+        N = Bt.shape[0]
+        e = GemmEpilogue(ctypes.c_float(alpha), _ptr(row_sub), int(bool(apply_exp)), _ptr(row_div),
+                         _ptr(row_max), _ptr(row_sum))
+        _check(lib.gb200_gemm_bf16_epilogue(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C),
+                                            _ld(C) if C is not None else 0, M, N, K, ctypes.byref(e),
+                                            _stream(stream)), "gb200_gemm_bf16_epilogue")
 
     def softmax_rows(self, x, out, stream=None, variant=None):
         rows, cols = x.shape

@@ -53,11 +53,42 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tn = r / rows_in_group;
 }
 
+// Consumers fused into the epilogue while the accumulator is still in TMEM / registers: the
+// reference's elementwise and row-reduction leaves applied to the product before it is rounded
+// (test/library/matrix/impl/cpu-matrix.h:134-194: exp_matrix, subtract_vec, divide_vec, max_row,
+// sum_row), in the order  t = alpha * acc;  t -= row_sub[i];  t = exp(t);  t /= row_div[i].
+struct GemmEpi {
+    float alpha;
+    const float *row_sub;
+    const float *row_div;
+    float *row_max;
+    float *row_sum;
+    int apply_exp;
+};
+
+// max over floats with integer atomics: non-negative values order like signed integers,
+// negative ones like unsigned integers in reverse; the target starts at -inf.
+__device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
+    if (v >= 0.0f)
+        atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
+    else
+        atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+
+__global__ void epilogue_init_kernel(float *row_max, float *row_sum, int M) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < M) {
+        if (row_max) row_max[i] = -INFINITY;
+        if (row_sum) row_sum[i] = 0.0f;
+    }
+}
+
+template <bool EPI>
 __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
                     int64_t ldc, int M, int N, int K, int splits, float *__restrict__ ws,
-                    int *status) {
+                    int *status, GemmEpi epi) {
     using namespace gemm;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -169,13 +200,33 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int row = tm * BM + lane_group * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                    static_cast<uint32_t>(buf * BN);
+            float e_sub = 0.0f, e_inv = 1.0f, e_max = -INFINITY, e_sum = 0.0f;
+            if (EPI && row < M) {
+                if (epi.row_sub) e_sub = epi.row_sub[row];
+                if (epi.row_div) e_inv = 1.0f / epi.row_div[row];
+            }
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + ch * 32, r);
                 tmem_ld_wait();
                 const int col = tn * BN + ch * 32;
-                if (splits > 1) {
+                if (EPI) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = fmaf(__uint_as_float(r[j]), epi.alpha, -e_sub);
+                        if (epi.apply_exp) v = __expf(v);
+                        v *= e_inv;
+                        r[j] = __float_as_uint(v);
+                        if (col + j < N) {
+                            e_max = fmaxf(e_max, v);
+                            e_sum += v;
+                        }
+                    }
+                }
+                if (EPI && C == nullptr) {
+                    // reductions only: the product itself is a temporary that is never stored
+                } else if (splits > 1) {
                     // fp32 partial sums into slab `split` of the workspace ([splits][M][N])
                     if (row < M && col < N) {
                         float *dst = ws + (static_cast<int64_t>(split) * M + row) * N + col;
@@ -213,6 +264,11 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (EPI && row < M) {
+                // one atomic per row and tile: the tiles of a row meet in the output vectors
+                if (epi.row_max) atomic_max_f32(epi.row_max + row, e_max);
+                if (epi.row_sum) atomicAdd(epi.row_sum + row, e_sum);
+            }
         }
     }
 
@@ -335,11 +391,11 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     }
     const int64_t items = n_tiles * splits;
     const int grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
-    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel,
+    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<false>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_bf16_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+    gemm_bf16_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
         ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, splits, ws,
-        ctx->d_status);
+        ctx->d_status, GemmEpi{});
     rc = after_launch(ctx, "gemm_bf16_tc_kernel");
     if (rc || splits == 1) return rc;
     const int64_t groups = M * ((N + 3) / 4);
@@ -350,11 +406,70 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     return after_launch(ctx, "gemm_splitk_reduce_kernel");
 }
 
+// GEMM with consumers fused into the epilogue (single-CTA tiles, no split-K: the reductions and
+// the exponential need the complete dot product).
+int gemm_bf16_epilogue_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B,
+                                int64_t ldb, void *C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                                const GemmEpi &epi, cudaStream_t stream) {
+    using namespace gemm;
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    GB200_REQUIRE(ctx->encode_tiled != nullptr, GB200_ERR_NO_DEVICE, "TMA descriptors unavailable");
+    GB200_REQUIRE(al16(A) && al16(B) && lda % 8 == 0 && ldb % 8 == 0, GB200_ERR_UNSUPPORTED,
+                  "gemm epilogue: A and B need 16-byte aligned rows (base and leading dimension)");
+    if (epi.row_max || epi.row_sum) {
+        epilogue_init_kernel<<<(unsigned)((M + 255) / 256), 256, 0, stream>>>(epi.row_max, epi.row_sum, (int)M);
+        int rc0 = after_launch(ctx, "epilogue_init_kernel");
+        if (rc0) return rc0;
+    }
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
+                         (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
+                     (uint64_t)ldb * 2, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
+    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<true>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    gemm_bf16_tc_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, 1, nullptr,
+        ctx->d_status, epi);
+    return after_launch(ctx, "gemm_bf16_tc_kernel<epilogue>");
+}
+
 }  // namespace gb200
 
 using namespace gb200;
 
 extern "C" {
+
+int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                             void *C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                             const gb200_gemm_epilogue *e, void *stream) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(e != nullptr, GB200_ERR_INVALID_ARG, "epilogue description is NULL");
+    GB200_REQUIRE(C != nullptr || e->row_max != nullptr || e->row_sum != nullptr, GB200_ERR_INVALID_ARG,
+                  "nothing to produce: C, row_max and row_sum are all NULL");
+    GB200_REQUIRE(M >= 0 && N >= 0 && K >= 0, GB200_ERR_INVALID_ARG, "negative extent");
+    GB200_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), GB200_ERR_UNSUPPORTED,
+                  "extent beyond 2^31");
+    if (M == 0 || N == 0) return GB200_OK;
+    GB200_REQUIRE(K > 0, GB200_ERR_UNSUPPORTED, "gemm epilogue: K must be positive");
+    GB200_REQUIRE(A != nullptr && B != nullptr, GB200_ERR_INVALID_ARG, "NULL matrix pointer");
+    GB200_REQUIRE(lda >= K && ldb >= K && (C == nullptr || ldc >= N), GB200_ERR_INVALID_ARG,
+                  "leading dimension smaller than the row");
+    GemmEpi epi;
+    epi.alpha = e->alpha;
+    epi.row_sub = e->row_sub;
+    epi.row_div = e->row_div;
+    epi.row_max = e->row_max;
+    epi.row_sum = e->row_sum;
+    epi.apply_exp = e->apply_exp;
+    return gemm_bf16_epilogue_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, epi,
+                                       static_cast<cudaStream_t>(stream));
+}
 
 int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                     void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream) {
@@ -429,7 +544,7 @@ int static_setup(int device, StaticDeviceState **out) {
         GB200_REQUIRE(q == cudaDriverEntryPointSuccess && fn != nullptr, GB200_ERR_NO_DEVICE,
                       "cuTensorMapEncodeTiled is not available from this driver");
         st.encode = reinterpret_cast<gb200::EncodeTiledFn>(fn);
-        GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel,
+        GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<false>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             gemm::SMEM_BYTES));
         st.ready = true;
@@ -487,9 +602,9 @@ int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int
     const int grid = (int)(items < st->sm_count ? items : st->sm_count);
     // Every (tile, split) item overwrites its whole region of the slabs, so nothing left in the
     // array by an earlier call is ever read; the status word is only ever set, never relied on.
-    gemm_bf16_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
+    gemm_bf16_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
         ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, splits,
-        splits > 1 ? st->ws : nullptr, st->status);
+        splits > 1 ? st->ws : nullptr, st->status, GemmEpi{});
     cudaError_t err = cudaPeekAtLastError();
     GB200_REQUIRE(err == cudaSuccess, GB200_ERR_CUDA, "launch failed: %s", cudaGetErrorString(err));
     if (splits > 1) {

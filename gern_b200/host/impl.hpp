@@ -86,6 +86,30 @@ public:
     Datatype dtype;
 };
 
+// fp32 vector in device memory: the row vectors of the softmax pieces (max, sum, and the operands
+// of subtract_vec / divide_vec), the reference's impl::ArrayGPU / StaticArray.
+class ArrayGPU {
+public:
+    explicit ArrayGPU(int64_t size) : size(size) {
+        cudaCheck(cudaMalloc(reinterpret_cast<void **>(&data), sizeof(float) * (size > 0 ? size : 1)), "cudaMalloc");
+    }
+    void put(const std::vector<float> &h) {
+        if (static_cast<int64_t>(h.size()) != size) throw error::UserError("ArrayGPU::put: size mismatch");
+        cudaCheck(cudaMemcpy(data, h.data(), sizeof(float) * size, cudaMemcpyHostToDevice), "cudaMemcpy");
+    }
+    std::vector<float> get() const {
+        std::vector<float> h(size);
+        cudaCheck(cudaMemcpy(h.data(), data, sizeof(float) * size, cudaMemcpyDeviceToHost), "cudaMemcpy");
+        return h;
+    }
+    void destroy() {
+        if (data) cudaFree(data);
+        data = nullptr;
+    }
+    float *data = nullptr;
+    int64_t size;
+};
+
 }  // namespace impl
 }  // namespace b200
 }  // namespace gern

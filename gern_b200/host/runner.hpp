@@ -11,6 +11,8 @@
 //     max ; subtract ; exp ; sum ; divide on one matrix  -> gb200_softmax_rows_f32
 //     matrix_multiply ; the softmax chain ; matrix_multiply through temporaries
 //                                                        -> gb200_attention_bf16
+//     matrix_multiply ; [subtract_vec] ; [exp_matrix] ; [divide_vec] ; [max_row] ; [sum_row] on
+//     its product (bf16 operands)                        -> gb200_gemm_bf16_epilogue
 // Anything else is a UserError: there is no generic code generator and no fallback behind this
 // Runner.  evaluate() performs the reference's argument checks (every ADT of the program must be
 // supplied by name, nothing else may be) and makes one C-ABI call.
@@ -42,7 +44,7 @@ public:
         std::string arch = "";
     };
 
-    enum class Kernel { None, GemmF32, GemmBF16, Blur, Softmax, Attention };
+    enum class Kernel { None, GemmF32, GemmBF16, Blur, Softmax, Attention, GemmEpilogue };
 
     void compile() { compile(Options{}); }
     void compile(Options config) {
@@ -105,6 +107,29 @@ public:
                 require(Q.col == K.col && K.row == V.row && O.row == Q.row && O.col == V.col, "attention: shapes do not agree");
                 rc = gb200_attention_bf16(ctx, Q.data, Q.lda, K.data, K.lda, V.data, V.lda, O.data, O.lda,
                                           Q.row, K.row, Q.col, scale, nullptr);
+                break;
+            }
+            case Kernel::GemmEpilogue: {
+                auto V = [&](const std::string &n) -> float * {
+                    return n.empty() ? nullptr : static_cast<impl::ArrayGPU *>(args.at(n))->data;
+                };
+                auto &A = M(names[0]), &B = M(names[1]);
+                impl::MatrixGPU *C = epi_c.empty() ? nullptr : &M(epi_c);
+                require(A.col == B.col, "matrix_multiply: shapes do not agree");
+                if (C) require(C->row == A.row && C->col == B.row, "matrix_multiply: shapes do not agree");
+                for (const std::string *v : {&epi_sub, &epi_div, &epi_max, &epi_sum})
+                    if (!v->empty())
+                        require(static_cast<impl::ArrayGPU *>(args.at(*v))->size == A.row,
+                                "row vector length differs from the number of rows");
+                gb200_gemm_epilogue e;
+                e.alpha = scale;
+                e.row_sub = V(epi_sub);
+                e.apply_exp = epi_exp ? 1 : 0;
+                e.row_div = V(epi_div);
+                e.row_max = V(epi_max);
+                e.row_sum = V(epi_sum);
+                rc = gb200_gemm_bf16_epilogue(ctx, A.data, A.lda, B.data, B.lda, C ? C->data : nullptr,
+                                              C ? C->lda : 0, A.row, B.row, A.col, &e, nullptr);
                 break;
             }
             default: throw error::InternalError("no kernel planned");
@@ -202,7 +227,7 @@ private:
             }
             plan = Kernel::Blur;
             names = {calls[0].inputs[0].getName(), calls[1].output.getName()};
-        } else if (calls.size() == 5) {
+        } else if (calls.size() == 5 && calls[0].op != Op::MatrixMultiply) {
             AbstractDataTypePtr in, out;
             if (!isChain(0, in, out)) throw error::UserError("unrecognised 5-call pipeline (expected the softmax chain)");
             plan = Kernel::Softmax;
@@ -217,6 +242,8 @@ private:
             plan = Kernel::Attention;
             scale = calls[0].scale;
             names = {Q.getName(), K.getName(), V.getName(), O.getName()};
+        } else if (calls.size() >= 2 && calls.size() <= 6 && calls[0].op == Op::MatrixMultiply) {
+            lowerEpilogue(f32);
         } else {
             std::ostringstream os;
             os << "no fused sm_100a kernel for this pipeline:";
@@ -230,6 +257,61 @@ private:
         if (uniq.size() != argument_order.size()) throw error::UserError("two arguments share a name");
     }
 
+    // matrix_multiply followed by consumers of its product: elementwise leaves in the order
+    // subtract_vec, exp_matrix, divide_vec (each optional), then max_row and / or sum_row of the
+    // last matrix.  Matrices between the stages must be temporaries (they live in TMEM and
+    // registers only); the last one is stored unless it is a temporary too.
+    template <typename F32>
+    void lowerEpilogue(F32 f32) {
+        const auto &mm = calls[0];
+        const auto &A = mm.inputs[0], &B = mm.inputs[1];
+        if (f32(A) || f32(B)) throw error::UserError("fused consumers need the BFloat16 matrix_multiply");
+        if (B->getLayout() != Layout::ColMajor) throw error::UserError("bf16 matrix_multiply takes a column-major B");
+        epi_sub = epi_div = epi_max = epi_sum = epi_c = "";
+        epi_exp = false;
+        AbstractDataTypePtr cur = mm.output;
+        size_t at = 1;
+        auto step = [&](const AbstractDataTypePtr &next) {
+            if (!cur->isTemporary())
+                throw error::UserError("matrix " + cur.getName() + " sits between fused stages: declare it a temporary");
+            cur = next;
+            ++at;
+        };
+        if (at < calls.size() && calls[at].op == Op::SubstractVec && calls[at].inputs[1] == cur) {
+            epi_sub = calls[at].inputs[0].getName();
+            step(calls[at].output);
+        }
+        if (at < calls.size() && calls[at].op == Op::ExpMatrix && calls[at].inputs[0] == cur) {
+            epi_exp = true;
+            step(calls[at].output);
+        }
+        if (at < calls.size() && calls[at].op == Op::DivideVec && calls[at].inputs[1] == cur) {
+            epi_div = calls[at].inputs[0].getName();
+            step(calls[at].output);
+        }
+        for (; at < calls.size(); ++at) {
+            const auto &cl = calls[at];
+            if (cl.op == Op::MaxRow && cl.inputs[0] == cur && epi_max.empty())
+                epi_max = cl.output.getName();
+            else if (cl.op == Op::SumRow && cl.inputs[0] == cur && epi_sum.empty())
+                epi_sum = cl.output.getName();
+            else
+                throw error::UserError(std::string("no fused sm_100a kernel: ") + opName(cl.op) +
+                                       " cannot follow in the epilogue of matrix_multiply here");
+        }
+        if (f32(cur) && !cur->isTemporary()) throw error::UserError("the stored result of the fused GEMM is BFloat16");
+        if (!cur->isTemporary()) epi_c = cur.getName();
+        if (epi_c.empty() && epi_max.empty() && epi_sum.empty())
+            throw error::UserError("the pipeline produces nothing: its last matrix is a temporary");
+        plan = Kernel::GemmEpilogue;
+        scale = mm.scale;
+        names = {A.getName(), B.getName()};
+        for (const std::string *v : {&epi_c, &epi_sub, &epi_div, &epi_max, &epi_sum})
+            if (!v->empty()) names.push_back(*v);
+    }
+
+    std::string epi_sub, epi_div, epi_max, epi_sum, epi_c;
+    bool epi_exp = false;
     Composable c;
     std::vector<FunctionCall> calls;
     Kernel plan = Kernel::None;

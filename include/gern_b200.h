@@ -79,6 +79,31 @@ int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, 
 int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                     void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream);
 
+/* bf16 GEMM whose consumers run in the epilogue, while the fp32 accumulator is still in TMEM /
+ * registers: the reference's elementwise and row-reduction leaves
+ * (test/library/matrix/impl/cpu-matrix.h:134-194; annotations test/library/matrix/annot/cpu-matrix.h:128-257)
+ * composed after annot::MatrixMultiply, generalising the GEMM -> softmax -> GEMM chain.  Per
+ * element (i,j) of the product, in this order:
+ *     t = alpha * (A B)(i,j);  t -= row_sub[i];  if (apply_exp) t = exp(t);  t /= row_div[i];
+ * then C(i,j) = bf16(t), row_max[i] = max_j t, row_sum[i] = sum_j t (from t before rounding).
+ * NULL vectors switch their step off; C may be NULL when only the reductions are wanted (the
+ * product is then a temporary that never reaches memory).  row_sub / row_div / row_max / row_sum
+ * are device vectors of M floats; the output vectors are initialised by the library.  Operand
+ * conventions as gb200_gemm_bf16; A and B must have 16-byte aligned rows.  subtract is `t - v`, as
+ * in the reference's GPU leaf (apps/common/impl/impl.h:53-78) and in the softmax it serves; the
+ * reference's CPU leaf computes `v - t` (cpu-matrix.h:170-181). */
+typedef struct gb200_gemm_epilogue {
+    float alpha;
+    const float *row_sub;
+    int apply_exp;
+    const float *row_div;
+    float *row_max;
+    float *row_sum;
+} gb200_gemm_epilogue;
+int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                             void *C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                             const gb200_gemm_epilogue *epilogue, void *stream);
+
 /* Split-K bf16 GEMM that allocates nothing and needs no context (same operand conventions as
  * gb200_gemm_bf16; `splits` = 1..16, or 0 to let the library choose).  It has no counterpart in
  * the reference.  It is for callers that cannot call cudaMalloc where they need the product: a

@@ -156,6 +156,22 @@ class Oracle:
         self.lib.oracle_gemm_bf16(_u16(a_bits), k, _u16(b_bits), k, _f(out), n, n, k, row_begin, row_end)
         return out
 
+    def gemm_bf16_epilogue(self, a_bits, b_bits, alpha=1.0, row_sub=None, apply_exp=False, row_div=None):
+        """The reference's leaves composed after the product, in the order the fused epilogue applies
+        them: t = alpha * (A B); t - row_sub (the GPU leaf's direction, apps/common/impl/impl.h:53-78);
+        exp_matrix (cpu-matrix.h:134-144); divide_vec (cpu-matrix.h:183-194).  Returns the fp32 matrix
+        t, its row maxima (max_row without the reference's FLT_MIN seed, cpu-matrix.h:158-168) and its
+        row sums (sum_row, cpu-matrix.h:146-156)."""
+        t = self.gemm_bf16(a_bits, b_bits) * np.float32(alpha)
+        if row_sub is not None:
+            t = (t - np.asarray(row_sub, np.float32)[:, None]).astype(np.float32)
+        if apply_exp:
+            t = self.exp_matrix(np.ascontiguousarray(t))
+        if row_div is not None:
+            t = self.divide_vec(np.asarray(row_div, np.float32), np.ascontiguousarray(t))
+        t = np.ascontiguousarray(t, dtype=np.float32)
+        return t, t.max(axis=1), self.sum_row(t)
+
     def attention_bf16(self, q_bits, k_bits, v_bits, scale, row_begin=0, row_end=None):
         nq, d = q_bits.shape
         nkv = k_bits.shape[0]

@@ -133,6 +133,32 @@ static AttentionProgram attentionProgram(float scale) {
     return p;
 }
 
+// matrix_multiply whose product feeds the reference's elementwise / row-reduction leaves:
+// E = exp(scale * A B - sub), with the row sums of E; the product and the difference are temporaries.
+struct EpilogueProgram {
+    AbstractDataTypePtr A, B, E, sub, sum;
+    Composable program;
+};
+static EpilogueProgram epilogueProgram(float scale, bool temporaries = true, bool store = true) {
+    EpilogueProgram p;
+    const Datatype bf = Datatype::BFloat16;
+    p.A = AbstractDataTypePtr(new const annot::MatrixGPU("A", bf));
+    p.B = AbstractDataTypePtr(new const annot::MatrixGPU("B", bf, Layout::ColMajor));
+    p.E = AbstractDataTypePtr(new const annot::MatrixGPU("E", bf, Layout::RowMajor, !store));
+    p.sub = AbstractDataTypePtr(new const annot::ArrayGPU("m", false));
+    p.sum = AbstractDataTypePtr(new const annot::ArrayGPU("s", false));
+    auto S = AbstractDataTypePtr(new const annot::MatrixGPU("S", Datatype::Float32, Layout::RowMajor, temporaries));
+    auto D = AbstractDataTypePtr(new const annot::MatrixGPU("D", Datatype::Float32, Layout::RowMajor, true));
+    annot::MatrixMultiply mm(scale);
+    annot::SubstractVec subtract_vec;
+    annot::ExpMatrix exp_matrix;
+    annot::SumRow sum_row;
+    Variable row("row");
+    p.program = {Global((Tile(p.sum["x"], row.bind(128)) || Grid::BLOCK_X)(
+        mm(p.A, p.B, S), subtract_vec(p.sub, S, D), exp_matrix(D, p.E), sum_row(p.E, p.sum)))};
+    return p;
+}
+
 // ---- CPU-only checks -------------------------------------------------------------------------
 static void cpuTests() {
     {   // lowering picks the kernel and orders arguments by name
@@ -168,6 +194,22 @@ static void cpuTests() {
         CHECK(run.kernel() == Runner::Kernel::Attention);
         CHECK((run.argumentOrder() == std::vector<std::string>{"K", "O", "Q", "V"}));
     }
+    {   // consumers of a product go into the GEMM's epilogue
+        auto p = epilogueProgram(0.25f);
+        Runner run(p.program);
+        run.compile();
+        CHECK(run.kernel() == Runner::Kernel::GemmEpilogue);
+        CHECK((run.argumentOrder() == std::vector<std::string>{"A", "B", "E", "m", "s"}));
+        auto q = epilogueProgram(0.25f, true, false);   // E a temporary: only the row sums leave the kernel
+        Runner run2(q.program);
+        run2.compile();
+        CHECK((run2.argumentOrder() == std::vector<std::string>{"A", "B", "m", "s"}));
+    }
+    CHECK(throwsUserError([] {   // a matrix between fused stages has nowhere to live unless it is a temporary
+        auto p = epilogueProgram(1.0f, false);
+        Runner run(p.program);
+        run.compile();
+    }));
     // errors, as the reference raises them
     CHECK(throwsUserError([] {   // evaluate before compile (src/codegen/runner.cpp:58-60)
         auto p = blurProgram();
@@ -345,6 +387,40 @@ static void gpuTests() {
             }
         CHECK(exact);
         A.destroy(); B.destroy(); C.destroy();
+    }
+    {   // exp(0.25 * A B - m) with row sums, against a CPU loop on the same small integers
+        const int64_t m = 160, n = 300, k = 64;
+        auto p = epilogueProgram(0.25f);
+        Runner run(p.program);
+        run.compile();
+        const Datatype bfd = Datatype::BFloat16;
+        impl::MatrixGPU A(m, k, k, bfd), B(n, k, k, bfd), E(m, n, 304, bfd);
+        impl::ArrayGPU sub(m), sum(m);
+        std::vector<uint16_t> ha(m * k), hb(n * k), he(m * 304);
+        std::vector<float> hsub(m);
+        auto bf = [](float f) { uint32_t u; std::memcpy(&u, &f, 4); return static_cast<uint16_t>(u >> 16); };
+        auto fl = [](uint16_t b) { uint32_t u = uint32_t(b) << 16; float f; std::memcpy(&f, &u, 4); return f; };
+        for (int64_t i = 0; i < m * k; i++) ha[i] = bf(static_cast<float>(int(i % 3) - 1));
+        for (int64_t i = 0; i < n * k; i++) hb[i] = bf(static_cast<float>(int(i % 5) - 2));
+        for (int64_t i = 0; i < m; i++) hsub[i] = 0.5f * static_cast<float>(i % 7);
+        A.put_raw(ha.data()); B.put_raw(hb.data()); sub.put(hsub);
+        run.evaluate({{"A", &A}, {"B", &B}, {"E", &E}, {"m", &sub}, {"s", &sum}});
+        E.get_raw(he.data());
+        const std::vector<float> hsum = sum.get();
+        bool ok = true;
+        for (int64_t i = 0; i < m; i++) {
+            float rs = 0.f;
+            for (int64_t j = 0; j < n; j++) {
+                float acc = 0.f;
+                for (int64_t kk = 0; kk < k; kk++) acc += fl(ha[i * k + kk]) * fl(hb[j * k + kk]);
+                const float want = std::exp(0.25f * acc - hsub[i]);
+                rs += want;
+                ok = ok && std::fabs(fl(he[i * 304 + j]) - want) <= 0.01f * want + 1e-6f;
+            }
+            ok = ok && std::fabs(hsum[i] - rs) <= 1e-3f * rs;
+        }
+        CHECK(ok);
+        A.destroy(); B.destroy(); E.destroy(); sub.destroy(); sum.destroy();
     }
     {   // fused chain with all-zero Q: uniform weights, O = column means of V
         const int64_t nq = 128, nkv = 256, d = 128;
