@@ -45,6 +45,51 @@ inline const char *name(Unit u) {
                               "BLOCK_CLUSTER_X", "BLOCK_CLUSTER_Y", "BLOCK_CLUSTER_Z"};
     return n[u];
 }
+// Launch dimensions a Global() may pin (include/gern/annotations/grid.h:31-45), with the cluster
+// dimensions the reference reserves a level for but never emits (grid.h:47-56).
+enum Dim {
+    GRID_DIM_X, GRID_DIM_Y, GRID_DIM_Z,
+    BLOCK_DIM_X, BLOCK_DIM_Y, BLOCK_DIM_Z,
+    WARP_DIM_X, WARP_DIM_Y, WARP_DIM_Z,
+    CLUSTER_DIM_X, CLUSTER_DIM_Y, CLUSTER_DIM_Z,
+    NULL_DIM,
+};
+enum Level { NULL_LEVEL = 0, SCALAR = 1, THREADS = 2, THREADS_WARPS = 3, WARPS = 4, BLOCK = 5, BLOCK_CLUSTER = 6, GRID = 7 };
+// src/annotations/grid.cpp:134-158, extended by the cluster units.
+inline Level getLevel(Unit u) {
+    switch (u) {
+        case THREAD_X: case THREAD_Y: case THREAD_Z: return THREADS;
+        case THREAD_X_IN_WRAPS: case THREAD_Y_IN_WRAPS: case THREAD_Z_IN_WRAPS: return THREADS_WARPS;
+        case WARP_X: case WARP_Y: case WARP_Z: return WARPS;
+        case BLOCK_X: case BLOCK_Y: case BLOCK_Z: return BLOCK;
+        case BLOCK_CLUSTER_X: case BLOCK_CLUSTER_Y: case BLOCK_CLUSTER_Z: return BLOCK_CLUSTER;
+        case SCALAR_UNIT: return SCALAR;
+        default: return NULL_LEVEL;
+    }
+}
+// The launch dimension a unit is counted in (src/annotations/grid.cpp:198-230): threads in the
+// block dimensions, warps too, blocks in the grid dimensions, clusters in the cluster dimensions.
+inline Dim getDim(Unit u) {
+    switch (u) {
+        case THREAD_X: case WARP_X: return BLOCK_DIM_X;
+        case THREAD_Y: case WARP_Y: return BLOCK_DIM_Y;
+        case THREAD_Z: case WARP_Z: return BLOCK_DIM_Z;
+        case THREAD_X_IN_WRAPS: return WARP_DIM_X;
+        case THREAD_Y_IN_WRAPS: return WARP_DIM_Y;
+        case THREAD_Z_IN_WRAPS: return WARP_DIM_Z;
+        case BLOCK_X: return GRID_DIM_X;
+        case BLOCK_Y: return GRID_DIM_Y;
+        case BLOCK_Z: return GRID_DIM_Z;
+        case BLOCK_CLUSTER_X: return CLUSTER_DIM_X;
+        case BLOCK_CLUSTER_Y: return CLUSTER_DIM_Y;
+        case BLOCK_CLUSTER_Z: return CLUSTER_DIM_Z;
+        default: return NULL_DIM;
+    }
+}
+inline const char *levelName(Level l) {
+    static const char *n[] = {"NULL_LEVEL", "SCALAR", "THREADS", "THREADS_WARPS", "WARPS", "BLOCK", "BLOCK_CLUSTER", "GRID"};
+    return n[l];
+}
 }  // namespace Grid
 
 // A named int64 variable; bind() fixes its value at program-construction time, as

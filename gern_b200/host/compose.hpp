@@ -41,6 +41,9 @@ struct Node {
     bool reduce = false;
     // Stage
     AbstractDataTypePtr staged;
+    // Global
+    std::map<Grid::Dim, Variable> launch_args;
+    Variable smem_size;
 };
 
 inline Composable::Composable(std::initializer_list<Composable> composed)
@@ -109,10 +112,17 @@ inline Composable Stage(AbstractDataTypePtr adt, Composable body) {
     return Composable(n);
 }
 
-inline Composable Global(Composable program) {
+// include/gern/compose/composable.h:49-52.  launch_args pins launch dimensions to bound variables
+// and smem_size asks for dynamic shared memory; both are checked (Runner::compile) and recorded,
+// but the kernels of libgern_b200 size their own grids, clusters and shared memory from the
+// run-time problem, so they do not steer a launch.
+inline Composable Global(Composable program, std::map<Grid::Dim, Variable> launch_args = {},
+                         Variable smem_size = Variable()) {
     auto n = std::make_shared<Node>();
     n->kind = Node::Global;
     n->children = {program};
+    n->launch_args = std::move(launch_args);
+    n->smem_size = std::move(smem_size);
     return Composable(n);
 }
 

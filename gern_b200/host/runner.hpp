@@ -51,6 +51,7 @@ public:
         if (!config.arch.empty() && config.arch != "100a")
             throw error::UserError("libgern_b200 holds sm_100a code only (arch=" + config.arch + ")");
         calls.clear();
+        launch_args.clear();
         std::set<int> units;
         bool in_global = false;
         flatten(c, units, in_global);
@@ -62,7 +63,13 @@ public:
     Kernel kernel() const { return plan; }
     std::vector<std::string> argumentOrder() const { return argument_order; }
 
-    void evaluate(std::map<std::string, void *> args) {
+    // Launch dimensions pinned by Global(), by dimension (checked, recorded, advisory).
+    const std::map<Grid::Dim, int64_t> &launchArgs() const { return launch_args; }
+
+    void evaluate(std::map<std::string, void *> args) { evaluate(std::move(args), nullptr); }
+    // `stream`: the CUDA stream the kernels are enqueued on (the reference's hook has none and
+    // launches on the legacy default stream, src/codegen/codegen.cpp:576-611; nullptr does the same).
+    void evaluate(std::map<std::string, void *> args, cudaStream_t stream) {
         if (!compiled) throw error::UserError("Please compile the pipeline first");
         if (args.size() != argument_order.size())
             throw error::UserError("All the arguments have not been passed! Expecting " +
@@ -78,35 +85,35 @@ public:
                 require(A.col == B.row && C.row == A.row && C.col == B.col, "matrix_multiply: shapes do not agree");
                 // The reference's leaf accumulates into C (c += sum): keep that.
                 rc = gb200_gemm_f32(ctx, (const float *)A.data, A.lda, (const float *)B.data, B.lda,
-                                    (float *)C.data, C.lda, C.row, C.col, A.col, 1, nullptr);
+                                    (float *)C.data, C.lda, C.row, C.col, A.col, 1, stream);
                 break;
             }
             case Kernel::GemmBF16: {
                 auto &A = M(names[0]), &B = M(names[1]), &C = M(names[2]);
                 // B is a column-major K x N matrix: its object holds N rows of K values.
                 require(A.col == B.col && C.row == A.row && C.col == B.row, "matrix_multiply: shapes do not agree");
-                rc = gb200_gemm_bf16(ctx, A.data, A.lda, B.data, B.lda, C.data, C.lda, C.row, C.col, A.col, nullptr);
+                rc = gb200_gemm_bf16(ctx, A.data, A.lda, B.data, B.lda, C.data, C.lda, C.row, C.col, A.col, stream);
                 break;
             }
             case Kernel::Blur: {
                 auto &in = M(names[0]), &out = M(names[1]);
                 require(in.row >= out.row + 2 && in.col >= out.col + 2, "blur: the input must exceed the output by 2 rows and columns");
                 rc = gb200_blur3x3_f32(ctx, (const float *)in.data, in.lda, out.row + 2, out.col + 2,
-                                       (float *)out.data, out.lda, nullptr);
+                                       (float *)out.data, out.lda, stream);
                 break;
             }
             case Kernel::Softmax: {
                 auto &in = M(names[0]), &out = M(names[1]);
                 require(in.row == out.row && in.col == out.col, "softmax: shapes do not agree");
                 rc = gb200_softmax_rows_f32(ctx, (const float *)in.data, in.lda, (float *)out.data, out.lda,
-                                            in.row, in.col, nullptr);
+                                            in.row, in.col, stream);
                 break;
             }
             case Kernel::Attention: {
                 auto &Q = M(names[0]), &K = M(names[1]), &V = M(names[2]), &O = M(names[3]);
                 require(Q.col == K.col && K.row == V.row && O.row == Q.row && O.col == V.col, "attention: shapes do not agree");
                 rc = gb200_attention_bf16(ctx, Q.data, Q.lda, K.data, K.lda, V.data, V.lda, O.data, O.lda,
-                                          Q.row, K.row, Q.col, scale, nullptr);
+                                          Q.row, K.row, Q.col, scale, stream);
                 break;
             }
             case Kernel::GemmEpilogue: {
@@ -129,7 +136,7 @@ public:
                 e.row_max = V(epi_max);
                 e.row_sum = V(epi_sum);
                 rc = gb200_gemm_bf16_epilogue(ctx, A.data, A.lda, B.data, B.lda, C ? C->data : nullptr,
-                                              C ? C->lda : 0, A.row, B.row, A.col, &e, nullptr);
+                                              C ? C->lda : 0, A.row, B.row, A.col, &e, stream);
                 break;
             }
             default: throw error::InternalError("no kernel planned");
@@ -160,6 +167,15 @@ private:
                 return;
             case Node::Global:
                 if (in_global) throw error::UserError("Global inside Global");
+                for (const auto &kv : p->launch_args) {
+                    if (kv.first == Grid::NULL_DIM) throw error::UserError("Global: NULL_DIM cannot be pinned");
+                    if (!kv.second.isBound())
+                        throw error::UserError("Global: launch dimension bound to unbound variable " + kv.second.getName());
+                    if (kv.second.getInt64Val() <= 0) throw error::UserError("Global: launch dimensions are positive");
+                    launch_args[kv.first] = kv.second.getInt64Val();
+                }
+                if (p->smem_size.defined() && p->smem_size.isBound() && p->smem_size.getInt64Val() > 227 * 1024)
+                    throw error::UserError("Global: more dynamic shared memory than an sm_100a block can have (227 KB)");
                 flatten(p->children[0], units, true);
                 return;
             case Node::Stage: flatten(p->children[0], units, in_global); return;
@@ -169,6 +185,14 @@ private:
                     if (units.count(p->unit))
                         throw error::UserError(std::string("grid unit ") + Grid::name(p->unit) + " is bound twice in one nest");
                     if (!in_global) throw error::UserError("a grid unit can only be bound inside Global()");
+                    // Outer loops take the coarser units: what is already distributed inside must
+                    // not sit above the unit it is distributed over (legalToDistribute,
+                    // src/annotations/grid.cpp:121-132, checked at composable.cpp:247-258).
+                    for (int outer : units)
+                        if (Grid::getLevel(static_cast<Grid::Unit>(outer)) < Grid::getLevel(p->unit))
+                            throw error::UserError(std::string("Trying to distribute ") +
+                                                   Grid::levelName(Grid::getLevel(p->unit)) + " over unit " +
+                                                   Grid::name(static_cast<Grid::Unit>(outer)));
                     units.insert(p->unit);
                 }
                 if (!p->reduce && !p->member.adt.defined()) throw error::UserError("Tile needs an ADT field");
@@ -310,6 +334,7 @@ private:
             if (!v->empty()) names.push_back(*v);
     }
 
+    std::map<Grid::Dim, int64_t> launch_args;
     std::string epi_sub, epi_div, epi_max, epi_sum, epi_c;
     bool epi_exp = false;
     Composable c;

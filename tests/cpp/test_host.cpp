@@ -210,6 +210,44 @@ static void cpuTests() {
         Runner run(p.program);
         run.compile();
     }));
+    {   // cluster units nest above block units; Global() records pinned launch dimensions
+        auto A = AbstractDataTypePtr(new const annot::MatrixGPU("A", Datatype::BFloat16));
+        auto B = AbstractDataTypePtr(new const annot::MatrixGPU("B", Datatype::BFloat16, Layout::ColMajor));
+        auto C = AbstractDataTypePtr(new const annot::MatrixGPU("C", Datatype::BFloat16));
+        Variable cl("cl"), bx("bx"), by("by"), kd("k_dim"), kt("kt"), cx("cluster_x"), smem("smem");
+        annot::MatrixMultiply mm;
+        Composable prog = {Global(
+            (Tile(C["row"], cl.bind(256)) || Grid::BLOCK_CLUSTER_X)(
+                (Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(
+                    (Tile(C["col"], by.bind(256)) || Grid::BLOCK_Y)(
+                        (Reduce(kd, kt.bind(64)))(mm(A, B, C))))),
+            {{Grid::CLUSTER_DIM_X, cx.bind(2)}}, smem.bind(200 * 1024))};
+        Runner run(prog);
+        run.compile();
+        CHECK(run.kernel() == Runner::Kernel::GemmBF16);
+        CHECK(run.launchArgs().at(Grid::CLUSTER_DIM_X) == 2);
+        CHECK(Grid::getLevel(Grid::BLOCK_CLUSTER_Y) == Grid::BLOCK_CLUSTER);
+        CHECK(Grid::getDim(Grid::BLOCK_CLUSTER_Z) == Grid::CLUSTER_DIM_Z);
+        CHECK(throwsUserError([&] {   // blocks cannot be distributed over... a cluster inside a block
+            Composable bad = {Global(
+                (Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(
+                    (Tile(C["col"], cl.bind(256)) || Grid::BLOCK_CLUSTER_X)(mm(A, B, C))))};
+            Runner r(bad);
+            r.compile();
+        }));
+        CHECK(throwsUserError([&] {   // a pinned launch dimension needs a value
+            Composable bad = {Global((Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(A, B, C)),
+                                     {{Grid::GRID_DIM_X, Variable("gx")}})};
+            Runner r(bad);
+            r.compile();
+        }));
+        CHECK(throwsUserError([&] {   // more shared memory than an sm_100a block can have
+            Composable bad = {Global((Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(A, B, C)), {},
+                                     smem.bind(300 * 1024))};
+            Runner r(bad);
+            r.compile();
+        }));
+    }
     // errors, as the reference raises them
     CHECK(throwsUserError([] {   // evaluate before compile (src/codegen/runner.cpp:58-60)
         auto p = blurProgram();
@@ -307,6 +345,19 @@ static void gpuTests() {
         for (int64_t i = 0; i < rows; i++)
             for (int64_t j = 0; j < cols; j++) equal = equal && got(i, j) == by(i, j);
         CHECK(equal);
+        // the same program on a stream of the caller's: identical result once that stream is done
+        cudaStream_t stream;
+        impl::cudaCheck(cudaStreamCreate(&stream), "cudaStreamCreate");
+        out.vvals(0.0f);
+        run.evaluate({{p.input.getName(), &in}, {p.output.getName(), &out}}, stream);
+        impl::cudaCheck(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        auto again = out.get();
+        bool same = true;
+        for (int64_t i = 0; i < rows; i++)
+            for (int64_t j = 0; j < cols; j++) same = same && again(i, j) == by(i, j);
+        CHECK(same);
+        impl::cudaCheck(cudaStreamDestroy(stream), "cudaStreamDestroy");
+        again.destroy();
         got.destroy(); hin.destroy(); bx.destroy(); by.destroy(); in.destroy(); out.destroy();
     }
     {   // fp32 matmul, ascending % 10 inputs, |delta| < 1e-3 (gernels/mm/kernel_10.cu:140-177)
