@@ -551,7 +551,11 @@ def run_reference_arm(args, rank, world):
             times.append(dt)
     per = sum(times) / len(times)
     value = units / per / scale_of(cls.unit)
-    cfg = {"workload": WORKLOADS[args.workload].name, "sample": sample}
+    # the configuration this arm stands beside: the library arm's, word for word
+    shell = cls.__new__(cls)
+    shell.world = world
+    shell.mode = "peer loads over NVLink (symmetric memory)"
+    cfg = cls.config(shell)
     line = {"impl": "reference", "metric": cls.metric, "value": value, "unit": cls.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": cls.dtype, "data": "synthetic", "config": cfg,
