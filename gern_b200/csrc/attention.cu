@@ -166,6 +166,10 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Launched with launch_pdl: barrier set-up and the TMEM allocation above may overlap the tail
+    // of the previous kernel of the stream; no global memory is touched before it has completed.
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 9) {
         // ---------------- TMA producer ----------------
@@ -468,9 +472,9 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     const float scale_log2 = scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)((nq + BM * TILES - 1) / (BM * TILES));
-    attention_bf16_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
-        tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv, scale_log2,
-        ctx->d_status);
+    GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream,
+                              tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv,
+                              scale_log2, ctx->d_status));
     return after_launch(ctx, "attention_bf16_kernel");
 }
 

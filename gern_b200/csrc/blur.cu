@@ -167,6 +167,9 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict
 // reference's emitted kernel (per-thread register patch, apps/blur/blur.cu:19-45), minus its
 // redundant read of the output tile and with 4 columns per thread.
 // ---------------------------------------------------------------------------------------
+#ifndef GB200_BLUR_STCS
+#define GB200_BLUR_STCS 0
+#endif
 template <int ROWS>
 __global__ void __launch_bounds__(128)
 blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
@@ -176,6 +179,10 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
     // are read from `halo` (which may be a peer GPU's memory; ordinary loads only).
     const int out_cols = in_cols - 2;
     const int c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
+    // Launched with programmatic stream serialisation: blocks may become resident while the
+    // previous kernel of the stream drains; nothing is read before that kernel has completed.
+    pdl_launch_dependents();
+    pdl_wait();
     if (c0 >= out_cols) return;
     // With a halo the block rows run bottom-up, so that the few blocks that read the (possibly
     // remote, high-latency) halo rows start first and finish under the rest of the kernel.
@@ -198,9 +205,18 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
 #pragma unroll
         for (int r = 0; r < ROWS + 2; ++r) hpass4(a[r], b[r], ta[r], tb[r]);
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r)
-            *reinterpret_cast<ulonglong2 *>(dst + r * out_ld) = make_ulonglong2(
-                vpass2(ta[r], ta[r + 1], ta[r + 2]), vpass2(tb[r], tb[r + 1], tb[r + 2]));
+        for (int r = 0; r < ROWS; ++r) {
+            const ulonglong2 o = make_ulonglong2(vpass2(ta[r], ta[r + 1], ta[r + 2]),
+                                                 vpass2(tb[r], tb[r + 1], tb[r + 2]));
+#if GB200_BLUR_STCS
+            // the output is never read again: streaming stores leave L2 to the input rows
+            __stcs(reinterpret_cast<float4 *>(dst + r * out_ld),
+                   make_float4(__uint_as_float((uint32_t)o.x), __uint_as_float((uint32_t)(o.x >> 32)),
+                               __uint_as_float((uint32_t)o.y), __uint_as_float((uint32_t)(o.y >> 32))));
+#else
+            *reinterpret_cast<ulonglong2 *>(dst + r * out_ld) = o;
+#endif
+        }
     } else {
         // ragged bottom or right edge, or output rows that are not 16-byte aligned
         uint64_t t0a = 0, t0b = 0, t1a = 0, t1b = 0;
@@ -356,10 +372,9 @@ static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
                       const float *halo = nullptr, int64_t halo_ld = 0) {
     const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
     dim3 grid((unsigned)((out_cols + 511) / 512), (unsigned)((out_rows + ROWS - 1) / ROWS));
-    blur3x3_reg_kernel<ROWS><<<grid, 128, 0, stream>>>(
-        in, in_ld, (int)in_cols, out, out_ld, (int)out_rows,
-        (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, (int)(halo ? in_rows - 2 : in_rows), halo,
-        halo_ld);
+    GB200_CUDA_TRY(launch_pdl(blur3x3_reg_kernel<ROWS>, grid, dim3(128), 0, stream, in, in_ld, (int)in_cols,
+                              out, out_ld, (int)out_rows, (aligned16(out) && out_ld % 4 == 0) ? 1 : 0,
+                              (int)(halo ? in_rows - 2 : in_rows), halo, halo_ld));
     return after_launch(ctx, "blur3x3_reg_kernel");
 }
 

@@ -9,7 +9,8 @@
 // barrier or shared memory is involved.  Rows longer than 1024 columns switch to a CTA per row
 // (softmax_cta_kernel) so that a thread holds at most 8 vectors and many warps stay resident.
 //
-// Numerics: expf (not __expf), true division, fp32 throughout.  The reference's pieces as
+// Numerics: expf (not __expf), one correctly rounded reciprocal of the row sum and a multiply per
+// element (within 2 ulp of the true quotient), fp32 throughout.  The reference's pieces as
 // written are not a usable definition (its CPU subtract_vec computes max - x,
 // cpu-matrix.h:178; max is seeded with FLT_MIN / 0, cpu-matrix.h:161, impl.h:144), so the
 // mathematically stated form above is what is implemented.
@@ -36,6 +37,8 @@ template <int NV>
 __global__ void __launch_bounds__(128)
 softmax_warp_kernel(const float *__restrict__ in, int64_t ld_in, float *__restrict__ out,
                     int64_t ld_out, int64_t rows, int cols) {
+    pdl_launch_dependents();   // launched with launch_pdl: see common.cuh
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t warp = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
@@ -69,12 +72,14 @@ softmax_warp_kernel(const float *__restrict__ in, int64_t ld_in, float *__restri
             }
         }
         s = warp_sum(s);
+        // one correctly rounded reciprocal per row, then multiplies: within 2 ulp of the quotient
+        const float inv = 1.0f / s;
         float4 *dst = reinterpret_cast<float4 *>(out + row * ld_out);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int idx = lane + 32 * i;
             if (idx < nvec)
-                __stcs(dst + idx, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
+                __stcs(dst + idx, make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv));
         }
     }
 }
@@ -91,6 +96,8 @@ softmax_cta_kernel(const float *__restrict__ in, int64_t ld_in, float *__restric
     constexpr int NW = THREADS / 32;
     __shared__ float red_max[2][NW];
     __shared__ float red_sum[2][NW];
+    pdl_launch_dependents();   // launched with launch_pdl: see common.cuh
+    pdl_wait();
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int nvec = cols >> 2;
     int parity = 0;
@@ -131,12 +138,13 @@ softmax_cta_kernel(const float *__restrict__ in, int64_t ld_in, float *__restric
         s = 0.0f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) s += red_sum[parity][w];
+        const float inv = 1.0f / s;   // see the warp kernel
         float4 *dst = reinterpret_cast<float4 *>(out + row * ld_out);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int idx = threadIdx.x + THREADS * i;
             if (idx < nvec)
-                __stcs(dst + idx, make_float4(v[i].x / s, v[i].y / s, v[i].z / s, v[i].w / s));
+                __stcs(dst + idx, make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv));
         }
     }
 }
@@ -185,24 +193,26 @@ softmax_block_kernel(const float *__restrict__ in, int64_t ld_in, float *__restr
 template <int NV>
 static int launch_warp(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out, int64_t ld_out,
                        int64_t rows, int64_t cols, cudaStream_t stream) {
-    // 4 rows in flight per CTA; enough CTAs to fill the machine, no more than there are rows.
+    // 4 rows per CTA (one per warp), one CTA per 4 rows: see launch_cta for why not persistent.
     int64_t blocks = (rows + 3) / 4;
-    const int64_t cap = (int64_t)ctx->sm_count * 16;
-    if (blocks > cap) blocks = cap;
-    softmax_warp_kernel<NV><<<(unsigned)blocks, 128, 0, stream>>>(in, ld_in, out, ld_out, rows,
-                                                                  (int)cols);
+    if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
+    GB200_CUDA_TRY(launch_pdl(softmax_warp_kernel<NV>, dim3((unsigned)blocks), dim3(128), 0, stream, in,
+                              ld_in, out, ld_out, rows, (int)cols));
     return after_launch(ctx, "softmax_warp_kernel");
 }
 
 template <int NV, int THREADS>
 static int launch_cta(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out, int64_t ld_out,
                       int64_t rows, int64_t cols, cudaStream_t stream) {
-    int per_sm = 2048 / THREADS;  // resident CTAs per SM by thread count
-    if (per_sm > 16) per_sm = 16;
-    int64_t blocks = (int64_t)ctx->sm_count * per_sm;
+    // One row per CTA, not a persistent grid: the block scheduler refills an SM as soon as a row
+    // is done, which keeps more loads in flight than CTAs that loop over rows (measured at
+    // 65536 x 4096 with 16 / 32 / 64 / 128 looping CTAs per SM and with one CTA per row:
+    // 6169 / 6435 / 6612 / 6722 / 6858 GB/s).  The loop in the kernel covers grids capped below.
+    int64_t blocks = rows;
+    if (blocks > 0x7fffffffll) blocks = 0x7fffffffll;
     if (blocks > rows) blocks = rows;
-    softmax_cta_kernel<NV, THREADS><<<(unsigned)blocks, THREADS, 0, stream>>>(in, ld_in, out, ld_out,
-                                                                              rows, (int)cols);
+    GB200_CUDA_TRY(launch_pdl(softmax_cta_kernel<NV, THREADS>, dim3((unsigned)blocks), dim3(THREADS), 0,
+                              stream, in, ld_in, out, ld_out, rows, (int)cols));
     return after_launch(ctx, "softmax_cta_kernel");
 }
 
