@@ -320,20 +320,41 @@ class GemmBf16Workload(Workload):
     bound = "tensor"
     kernel = "gemm_bf16_2cta_kernel"
     N = 8192
+    SHAPE = None        # (M, N, K) from --shape: a kernel-only side measurement, not the headline
+    VS_CUBLAS = False   # --vs-cublas: time torch.matmul (cuBLAS) on the same operands beside it
 
     def __init__(self, ctx, rank, world, torch, dist=None):
         super().__init__(ctx, rank, world, torch)
-        n = self.N
+        m, n, k = self.SHAPE if self.SHAPE else (self.N, self.N, self.N)
+        self.mnk = (m, n, k)
         g = torch.Generator(device="cuda").manual_seed(7 + rank)
-        self.a = (torch.randn((n, n), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
-        self.b = (torch.randn((n, n), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
-        self.c = torch.empty((n, n), dtype=torch.bfloat16, device="cuda")
+        self.a = (torch.randn((m, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        self.b = (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        self.c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
 
     def units_per_step(self):
-        return 2.0 * self.N ** 3
+        m, n, k = self.mnk
+        return 2.0 * m * n * k
 
     def step(self, stream):
         self.ctx.gemm_bf16(self.a, self.b, self.c, stream=stream)
+
+    def library_baseline(self, steps, warmup):
+        """cuBLAS through torch.matmul on the same operands, timed like the kernel above."""
+        torch = self.torch
+        bt = self.b.T
+        for _ in range(warmup):
+            torch.matmul(self.a, bt, out=self.c)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            torch.matmul(self.a, bt, out=self.c)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"library": "cuBLAS via torch.matmul", "ms_per_step": ms,
+                "value": self.units_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
 
     def e2e_setup(self):
         torch = self.torch
@@ -351,6 +372,10 @@ class GemmBf16Workload(Workload):
 
     def config(self):
         n = self.N
+        if self.SHAPE:
+            m, n2, k = self.SHAPE
+            return {"workload": f"bf16 GEMM M={m} N={n2} K={k} per GPU (A row-major, B column-major, fp32 accumulate)",
+                    "sharding": "M panels, B replicated", "cache": "operands as they are (may fit L2)"}
         return {"workload": f"bf16 GEMM M=N=K={n} per GPU (A row-major, B column-major, fp32 accumulate)",
                 "sharding": "M panels, B replicated", "cache": "flush not needed: 384 MB of operands > L2"}
 
@@ -576,6 +601,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="reduced sizes (still larger than L2) for profiler captures; not a bench number")
+    ap.add_argument("--shape", default="", help="gemm_bf16 only: M,N,K of a side measurement (kernel only)")
+    ap.add_argument("--vs-cublas", action="store_true",
+                    help="gemm_bf16 only: add cuBLAS (torch.matmul) timed the same way under 'library'")
     ap.add_argument("--also", default="softmax,gemm_bf16,attention",
                     help="comma list of further workloads summarised under 'also' (N=1 only)")
     args = ap.parse_args()
@@ -605,6 +633,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.shape:
+        GemmBf16Workload.SHAPE = tuple(int(v) for v in args.shape.split(","))
+        args.no_e2e = args.no_cpu_baseline = True
+    GemmBf16Workload.VS_CUBLAS = args.vs_cublas
     if args.small:
         SoftmaxWorkload.ROWS = 16384
         GemmBf16Workload.N = 4096
@@ -674,6 +706,8 @@ def main():
                             "peak_source": peaks["source"], "kernel": wl.kernel,
                             "kernel_ms": per_launch_ms},
                "gpu_launches": launches, "clocks": clocks}
+        if getattr(wl, "VS_CUBLAS", False) and world == 1:
+            res["library"] = wl.library_baseline(steps, warmup)
         if want_e2e:
             h2d, d2h = wl.e2e_setup()
             e_steps = max(2, min(steps, 5))
@@ -723,6 +757,8 @@ def main():
             line["e2e"] = main_res["e2e"]
         if "cpu_baseline" in main_res:
             line["cpu_baseline"] = main_res["cpu_baseline"]
+        if "library" in main_res:
+            line["library"] = main_res["library"]
         if also:
             line["also"] = also
         print(json.dumps(line), flush=True)
