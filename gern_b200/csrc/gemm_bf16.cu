@@ -129,6 +129,9 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    // launched with launch_pdl: the set-up above may overlap the previous kernel's tail
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -284,6 +287,8 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
 __global__ void __launch_bounds__(256)
 gemm_splitk_reduce_kernel(const float *__restrict__ ws, int splits, __nv_bfloat16 *__restrict__ C,
                           int64_t ldc, int M, int N) {
+    pdl_launch_dependents();   // launched with launch_pdl right behind the GEMM kernel: its blocks
+    pdl_wait();                // are resident and waiting when the last slab is written
     const int64_t groups_per_row = (N + 3) / 4;
     const int64_t total = static_cast<int64_t>(M) * groups_per_row;
     const int64_t slab = static_cast<int64_t>(M) * N;
@@ -393,16 +398,17 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     const int grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
     GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<false>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_bf16_tc_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
-        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, splits, ws,
-        ctx->d_status, GemmEpi{});
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_tc_kernel<false>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+                              stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K,
+                              splits, ws, ctx->d_status, GemmEpi{}));
     rc = after_launch(ctx, "gemm_bf16_tc_kernel");
     if (rc || splits == 1) return rc;
     const int64_t groups = M * ((N + 3) / 4);
     int64_t blocks = (groups + 255) / 256;
     if (blocks > (int64_t)ctx->sm_count * 8) blocks = (int64_t)ctx->sm_count * 8;
-    gemm_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
-        ws, splits, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N);
+    GB200_CUDA_TRY(launch_pdl(gemm_splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
+                              static_cast<const float *>(ws), splits, static_cast<__nv_bfloat16 *>(C), ldc,
+                              (int)M, (int)N));
     return after_launch(ctx, "gemm_splitk_reduce_kernel");
 }
 
@@ -432,9 +438,9 @@ int gemm_bf16_epilogue_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, cons
     const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
     GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<true>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_bf16_tc_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(
-        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, 1, nullptr,
-        ctx->d_status, epi);
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_tc_kernel<true>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+                              stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, 1,
+                              static_cast<float *>(nullptr), ctx->d_status, epi));
     return after_launch(ctx, "gemm_bf16_tc_kernel<epilogue>");
 }
 

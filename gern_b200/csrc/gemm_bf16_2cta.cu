@@ -89,6 +89,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
     tc_fence_after();
     const uint32_t tmem_base = *tmem_base_slot;
+    // launched with launch_pdl: the set-up above may overlap the previous kernel's tail
+    pdl_launch_dependents();
+    pdl_wait();
 
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
@@ -213,8 +216,9 @@ int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void
     if (pairs > n_tiles) pairs = n_tiles;
     GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_2cta_kernel,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    gemm_bf16_2cta_kernel<<<(unsigned)(2 * pairs), NUM_THREADS, SMEM_BYTES, stream>>>(
-        ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, ctx->d_status);
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+                              (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
+                              (int)N, (int)K, ctx->d_status));
     return after_launch(ctx, "gemm_bf16_2cta_kernel");
 }
 
