@@ -160,23 +160,31 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try_wait may park the thread in hardware for up to this long; it resumes as soon as the
+// phase completes.  A parked thread takes no issue slots from the warps that do the arithmetic,
+// and a long wait needs few polls.
+constexpr uint32_t kTryWaitHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return ok != 0;
 }
 // Bounded wait.  Returns false (after writing `code` to *status) if the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
-    // fast path: a few polls without touching the timer
-    for (int i = 0; i < 64; ++i)
+    // Fast path: polls without a clock.  Reading the wall-clock timer is a long-latency operation
+    // (a barrier that completes while the read is outstanding is noticed late, which showed as
+    // microseconds on the TMA -> MMA -> epilogue hand-offs of a short GEMM), so the timer is
+    // consulted only once a wait has outlasted any wait of a healthy pipeline.  Each poll is
+    // bounded by the hardware (at most the hint above).
+    for (int i = 0; i < 1024; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     while (true) {
