@@ -468,8 +468,8 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     rc = get_tmap_2d(ctx, V, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)d, (uint64_t)nkv,
                      (uint64_t)ldv * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tv);
     if (rc) return rc;
-    GB200_CUDA_TRY(cudaFuncSetAttribute(attention_bf16_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    rc = ensure_dynamic_smem(ctx, attention_bf16_kernel, SMEM_BYTES);
+    if (rc) return rc;
     const float scale_log2 = scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)((nq + BM * TILES - 1) / (BM * TILES));
     GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream,

@@ -452,8 +452,8 @@ int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void
     rc = get_tmap_2d(ctx, V, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)d, (uint64_t)nkv,
                      (uint64_t)ldv * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tv);
     if (rc) return rc;
-    GB200_CUDA_TRY(cudaFuncSetAttribute(attention_bf16_pair_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    rc = ensure_dynamic_smem(ctx, attention_bf16_pair_kernel, SMEM_BYTES);
+    if (rc) return rc;
     const float scale_log2 = scale * 1.4426950408889634f;
     const unsigned pairs = (unsigned)((nq + 2 * BM - 1) / (2 * BM));
     attention_bf16_pair_kernel<<<2 * pairs, NUM_THREADS, SMEM_BYTES, stream>>>(

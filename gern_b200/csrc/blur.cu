@@ -357,8 +357,10 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
     bands = (out_rows + rows_per_band - 1) / rows_per_band;
     const int64_t n_items = bands * n_strips;
     auto kern = blur3x3_tma_kernel<RS, S>;
-    GB200_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Cfg::SMEM_BYTES));
+    {
+        const int rc_attr = ensure_dynamic_smem(ctx, kern, Cfg::SMEM_BYTES);
+        if (rc_attr) return rc_attr;
+    }
     kern<<<(unsigned)((n_items + Cfg::WARPS - 1) / Cfg::WARPS), 128, Cfg::SMEM_BYTES, stream>>>(
         tm, out, out_ld, (int)out_rows, (int)out_cols, (int)rows_per_band, n_strips, (int)n_items,
         (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, ctx->d_status);

@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #include <map>
+#include <set>
 #include <mutex>
 #include <string>
 #include <tuple>
@@ -67,6 +68,7 @@ struct gb200_ctx {
     int64_t launches = 0;
     gb200::EncodeTiledFn encode_tiled = nullptr;
     std::map<gb200::TmapKey, CUtensorMap> tmaps;
+    std::set<const void *> smem_attr_done;   // kernels whose dynamic shared memory limit is raised
     std::mutex mu;
     // device status word written by kernels whose bounded waits ran out
     int *d_status = nullptr;
@@ -90,6 +92,17 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
 
 // Sets the device for the calling thread, as every entry point must before touching CUDA.
 int enter(gb200_ctx *ctx);
+// Raises a kernel's dynamic shared memory limit once per context (the attribute call costs a
+// microsecond of host time, which a loop of short launches would pay every iteration).
+template <typename Kernel>
+inline int ensure_dynamic_smem(gb200_ctx *ctx, Kernel kernel, int bytes) {
+    const void *key = reinterpret_cast<const void *>(kernel);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    if (ctx->smem_attr_done.count(key)) return GB200_OK;
+    GB200_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    ctx->smem_attr_done.insert(key);
+    return GB200_OK;
+}
 // Grows staging slot `slot` to at least `bytes`.
 int stage_reserve(gb200_ctx *ctx, int slot, size_t bytes);
 // Grows the context's kernel workspace to at least `bytes`.

@@ -396,8 +396,8 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     }
     const int64_t items = n_tiles * splits;
     const int grid = (int)(items < ctx->sm_count ? items : ctx->sm_count);
-    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<false>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_tc_kernel<false>, SMEM_BYTES);
+    if (rc) return rc;
     GB200_CUDA_TRY(launch_pdl(gemm_bf16_tc_kernel<false>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
                               stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K,
                               splits, ws, ctx->d_status, GemmEpi{}));
@@ -436,8 +436,8 @@ int gemm_bf16_epilogue_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, cons
     if (rc) return rc;
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
-    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_tc_kernel<true>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_tc_kernel<true>, SMEM_BYTES);
+    if (rc) return rc;
     GB200_CUDA_TRY(launch_pdl(gemm_bf16_tc_kernel<true>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
                               stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K, 1,
                               static_cast<float *>(nullptr), ctx->d_status, epi));

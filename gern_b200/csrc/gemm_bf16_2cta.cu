@@ -214,8 +214,8 @@ int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int64_t pairs = ctx->sm_count / 2;
     if (pairs > n_tiles) pairs = n_tiles;
-    GB200_CUDA_TRY(cudaFuncSetAttribute(gemm_bf16_2cta_kernel,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel, SMEM_BYTES);
+    if (rc) return rc;
     GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                               (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
                               (int)N, (int)K, ctx->d_status));
