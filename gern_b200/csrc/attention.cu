@@ -405,6 +405,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             const float inv = 1.0f / l;
             const int row = q0 + t * BM + row_in_tile;
             const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(O) & 15) == 0);
+            const bool vec32_ok = (ldo % 16 == 0) && ((reinterpret_cast<uintptr_t>(O) & 31) == 0);
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t o[32];
@@ -412,7 +413,17 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 tmem_ld_wait();
                 if (row < nq) {
                     __nv_bfloat16 *dst = O + static_cast<int64_t>(row) * ldo + c * 32;
-                    if (vec_ok) {
+                    if (vec32_ok) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                w[i] = pack_bf16(__uint_as_float(o[16 * h + 2 * i]) * inv,
+                                                 __uint_as_float(o[16 * h + 2 * i + 1]) * inv);
+                            st_global_256(dst + 16 * h, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+                        }
+                    } else if (vec_ok) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint4 v;

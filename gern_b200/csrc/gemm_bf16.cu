@@ -191,6 +191,7 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t tile_it = 0;
         bool ok = true;
         const bool vec_ok = (ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(C) & 15) == 0);
+        const bool vec32_ok = (ldc % 16 == 0) && ((reinterpret_cast<uintptr_t>(C) & 31) == 0);
         for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++tile_it) {
             int tm, tn;
             tile_coords(t / splits, tiles_m, tiles_n, tm, tn);
@@ -247,7 +248,18 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 } else if (row < M && col < N) {
                     __nv_bfloat16 *dst = C + static_cast<int64_t>(row) * ldc + col;
-                    if (vec_ok && col + 32 <= N) {
+                    if (vec32_ok && col + 32 <= N) {
+                        // a thread owns 64 contiguous bytes of its row: two full 32-byte sectors
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                w[i] = pack_bf16(__uint_as_float(r[16 * h + 2 * i]),
+                                                 __uint_as_float(r[16 * h + 2 * i + 1]));
+                            st_global_256(dst + 16 * h, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+                        }
+                    } else if (vec_ok && col + 32 <= N) {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             uint4 v;
