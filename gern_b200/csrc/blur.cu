@@ -193,13 +193,29 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
     const float *src = in + static_cast<int64_t>(r_begin) * in_ld + c0;
     float *dst = out + static_cast<int64_t>(r_begin) * out_ld + c0;
     const bool local = r_begin + n_out + 2 <= in_rows_local;   // uniform over the block
-    if (n_out == ROWS && c0 + 6 <= in_cols && out_vec && local) {
+    // the block row that needs the halo takes the same vector path when the halo rows are
+    // 16-byte aligned: all its loads, the remote ones included, are in flight at once
+    const bool halo_vec = halo != nullptr && (reinterpret_cast<uintptr_t>(halo) & 15) == 0 && halo_ld % 4 == 0;
+    if (n_out == ROWS && c0 + 6 <= in_cols && out_vec && (local || halo_vec)) {
         float4 a[ROWS + 2];
         float2 b[ROWS + 2];
+        if (local) {
 #pragma unroll
-        for (int r = 0; r < ROWS + 2; ++r) {
-            a[r] = __ldg(reinterpret_cast<const float4 *>(src + r * in_ld));
-            b[r] = __ldg(reinterpret_cast<const float2 *>(src + r * in_ld + 4));
+            for (int r = 0; r < ROWS + 2; ++r) {
+                a[r] = __ldg(reinterpret_cast<const float4 *>(src + r * in_ld));
+                b[r] = __ldg(reinterpret_cast<const float2 *>(src + r * in_ld + 4));
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < ROWS + 2; ++r) {
+                const int gr = r_begin + r;
+                // plain loads: the halo may be another GPU's memory
+                const float *rp = gr < in_rows_local
+                                      ? src + r * in_ld
+                                      : halo + static_cast<int64_t>(gr - in_rows_local) * halo_ld + c0;
+                a[r] = *reinterpret_cast<const float4 *>(rp);
+                b[r] = *reinterpret_cast<const float2 *>(rp + 4);
+            }
         }
         uint64_t ta[ROWS + 2], tb[ROWS + 2];
 #pragma unroll
