@@ -604,7 +604,7 @@ def main():
     ap.add_argument("--shape", default="", help="gemm_bf16 only: M,N,K of a side measurement (kernel only)")
     ap.add_argument("--vs-cublas", action="store_true",
                     help="gemm_bf16 only: add cuBLAS (torch.matmul) timed the same way under 'library'")
-    ap.add_argument("--also", default="softmax,gemm_bf16,attention",
+    ap.add_argument("--also", default="softmax,attention,gemm_bf16",
                     help="comma list of further workloads summarised under 'also' (N=1 only)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
