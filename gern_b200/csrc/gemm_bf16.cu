@@ -83,13 +83,20 @@ __global__ void epilogue_init_kernel(float *row_max, float *row_sum, int M) {
     }
 }
 
-template <bool EPI>
+// TILE_N: columns of C per tile (256 by default; 192 and 128 serve problems whose 256-wide tiles
+// would leave SMs idle, see pick_tile_n).
+template <bool EPI, int TILE_N = 256>
 __global__ void __launch_bounds__(gemm::NUM_THREADS, 1)
 gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
                     int64_t ldc, int M, int N, int K, int splits, float *__restrict__ ws,
                     int *status, GemmEpi epi) {
     using namespace gemm;
+    constexpr int BN = TILE_N;                        // these shadow the 256-wide defaults
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "tile width");
+    (void)B_BYTES;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -370,7 +377,51 @@ int pick_splits(int64_t n_tiles, int64_t k_blocks, int sm_count) {
 int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                           void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream);
 
-// kernel_choice: 0 = pick, 1 = single-CTA tiles, 2 = CTA-pair tiles.
+// Tile width for the single-CTA kernel: rounds of tiles over the SMs times the time of one tile
+// (tensor-bound at 256 and 192 columns, shared-memory-bound and a little slower per flop at 128).
+// 1000 x 3000: 96 tiles of 256 columns leave a third of the SMs idle, 128 tiles of 192 columns
+// fill one round with tiles that take three quarters of the time.
+static int pick_tile_n(int64_t M, int64_t N, int sm_count) {
+    const int64_t tiles_m = (M + gemm::BM - 1) / gemm::BM;
+    const int widths[3] = {256, 192, 128};
+    const int cost_per_tile[3] = {128, 96, 72};
+    int best = 256;
+    int64_t best_cost = -1;
+    for (int i = 0; i < 3; ++i) {
+        const int64_t tiles = tiles_m * ((N + widths[i] - 1) / widths[i]);
+        const int64_t cost = ((tiles + sm_count - 1) / sm_count) * cost_per_tile[i];
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best = widths[i];
+        }
+    }
+    return best;
+}
+
+template <int TILE_N>
+static int launch_tc_plain(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                           void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+    using namespace gemm;
+    constexpr int smem_bytes = STAGES * (A_BYTES + TILE_N * BK * 2) + 1024 + 256;
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
+                         (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
+                     (uint64_t)ldb * 2, BK, TILE_N, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + TILE_N - 1) / TILE_N);
+    const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_tc_kernel<false, TILE_N>, smem_bytes);
+    if (rc) return rc;
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_tc_kernel<false, TILE_N>, dim3(grid), dim3(NUM_THREADS),
+                              (size_t)smem_bytes, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
+                              (int)N, (int)K, 1, static_cast<float *>(nullptr), ctx->d_status, GemmEpi{}));
+    return after_launch(ctx, "gemm_bf16_tc_kernel");
+}
+
+// kernel_choice: 0 = pick, 1 = single-CTA 128 x 256 tiles, 2 = CTA-pair tiles, 3 / 4 = single-CTA
+// tiles of 192 / 128 columns.
 int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                        void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream,
                        int forced_splits = 0, int kernel_choice = 0) {
@@ -400,6 +451,12 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
                            (kernel_choice == 0 && GB200_GEMM_AUTO_PAIR && pair_tiles >= ctx->sm_count / 2);
     if (want_pair && splits == 1 && forced_splits <= 1)
         return gemm_bf16_2cta_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, stream);
+    if (splits == 1 && forced_splits <= 1 && kernel_choice != 1) {
+        const int tile_n = kernel_choice == 3 ? 192 : kernel_choice == 4 ? 128
+                                                                        : pick_tile_n(M, N, ctx->sm_count);
+        if (tile_n == 192) return launch_tc_plain<192>(ctx, A, lda, B, ldb, C, ldc, M, N, K, stream);
+        if (tile_n == 128) return launch_tc_plain<128>(ctx, A, lda, B, ldb, C, ldc, M, N, K, stream);
+    }
     float *ws = nullptr;
     if (splits > 1) {
         rc = workspace_reserve(ctx, (size_t)splits * M * N * sizeof(float));
