@@ -447,6 +447,66 @@ class AttentionWorkload(Workload):
         return 4.0 * rows * self.NKV * self.D / dt / 1e12, f"{rows} rows of Q against all {self.NKV} keys"
 
 
+class GemmF32ShapeWorkload(Workload):
+    """fp32 matmul at a shape given with --shape: a kernel-only side measurement (the headline fp32
+    configuration is 512^3, GemmF32Workload).  Large shapes run on the tensor cores through
+    three-way bf16 splits; --vs-cublas adds torch.matmul with tf32 switched off."""
+    name = "gemm_f32_shape"
+    metric = "fp32 matmul, FLOP per second"
+    unit = "TFLOP/s"
+    dtype = "f32"
+    bound = "tensor"
+    kernel = "gemm_bf16_tc_kernel"
+    SHAPE = (4096, 4096, 4096)
+    VS_CUBLAS = False
+
+    def __init__(self, ctx, rank, world, torch, dist=None):
+        super().__init__(ctx, rank, world, torch)
+        m, n, k = self.SHAPE
+        g = torch.Generator(device="cuda").manual_seed(11 + rank)
+        self.a = torch.rand((m, k), generator=g, device="cuda") * 2 - 1
+        self.b = torch.rand((k, n), generator=g, device="cuda") * 2 - 1
+        self.c = torch.zeros((m, n), device="cuda")
+
+    def units_per_step(self):
+        m, n, k = self.SHAPE
+        return 2.0 * m * n * k
+
+    def step(self, stream):
+        self.ctx.gemm_f32(self.a, self.b, self.c, stream=stream)
+
+    def library_baseline(self, steps, warmup):
+        torch = self.torch
+        old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            for _ in range(warmup):
+                torch.matmul(self.a, self.b, out=self.c)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                torch.matmul(self.a, self.b, out=self.c)
+            e1.record()
+            torch.cuda.synchronize()
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = old
+        ms = e0.elapsed_time(e1) / steps
+        return {"library": "cuBLAS fp32 (tf32 off) via torch.matmul", "ms_per_step": ms,
+                "value": self.units_per_step() / (ms * 1e-3) / 1e12, "unit": "TFLOP/s"}
+
+    def e2e_setup(self):
+        return 0, 0
+
+    def config(self):
+        m, n, k = self.SHAPE
+        return {"workload": f"fp32 matmul M={m} N={n} K={k} per GPU, uniform[-1,1) (replicas only)",
+                "sharding": "replicas only", "cache": "operands as they are (may fit L2)"}
+
+    def cpu_sample(self, oracle, ref):
+        return 0.0, "none"
+
+
 class GemmF32Workload(Workload):
     name = "gemm_f32"
     metric = "fp32 matmul 512^3, FLOP per second"
@@ -502,7 +562,7 @@ class GemmF32Workload(Workload):
 
 
 WORKLOADS = {w.name: w for w in (BlurWorkload, SoftmaxWorkload, GemmBf16Workload, AttentionWorkload,
-                                 GemmF32Workload)}
+                                 GemmF32Workload, GemmF32ShapeWorkload)}
 
 
 def scale_of(unit):
@@ -601,9 +661,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="reduced sizes (still larger than L2) for profiler captures; not a bench number")
-    ap.add_argument("--shape", default="", help="gemm_bf16 only: M,N,K of a side measurement (kernel only)")
+    ap.add_argument("--shape", default="", help="gemm_bf16 / gemm_f32: M,N,K of a side measurement (kernel only)")
     ap.add_argument("--vs-cublas", action="store_true",
-                    help="gemm_bf16 only: add cuBLAS (torch.matmul) timed the same way under 'library'")
+                    help="with --shape: add cuBLAS (torch.matmul) timed the same way under 'library'")
     ap.add_argument("--also", default="softmax,attention,gemm_bf16",
                     help="comma list of further workloads summarised under 'also' (N=1 only)")
     args = ap.parse_args()
@@ -635,8 +695,12 @@ def main():
 
     if args.shape:
         GemmBf16Workload.SHAPE = tuple(int(v) for v in args.shape.split(","))
+        GemmF32ShapeWorkload.SHAPE = GemmBf16Workload.SHAPE
         args.no_e2e = args.no_cpu_baseline = True
+        if args.workload == "gemm_f32":
+            args.workload = "gemm_f32_shape"
     GemmBf16Workload.VS_CUBLAS = args.vs_cublas
+    GemmF32ShapeWorkload.VS_CUBLAS = args.vs_cublas
     if args.small:
         SoftmaxWorkload.ROWS = 16384
         GemmBf16Workload.N = 4096

@@ -30,6 +30,7 @@ SIGNATURES = {
     "gb200_version": None,
     "gb200_launch_count": None,
     "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
+    "gb200_gemm_f32_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _int],
     "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
     "gb200_gemm_bf16_splitk": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
     "gb200_gemm_bf16_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
@@ -207,9 +208,14 @@ class Context:
         return int(lib.gb200_launch_count(self.handle))
 
     # ---- device entry points (torch CUDA tensors) ----
-    def gemm_f32(self, A, B, C, accumulate=False, stream=None):
+    def gemm_f32(self, A, B, C, accumulate=False, stream=None, variant=None):
         M, K = A.shape
         N = B.shape[1]
+        if variant is not None:
+            _check(lib.gb200_gemm_f32_variant(self.handle, _ptr(A), _ld(A), _ptr(B), _ld(B), _ptr(C), _ld(C),
+                                              M, N, K, int(bool(accumulate)), _stream(stream), int(variant)),
+                   "gb200_gemm_f32_variant")
+            return
         _check(lib.gb200_gemm_f32(self.handle, _ptr(A), _ld(A), _ptr(B), _ld(B), _ptr(C), _ld(C), M, N, K,
                                   int(bool(accumulate)), _stream(stream)), "gb200_gemm_f32")
 

@@ -64,6 +64,12 @@ struct GemmEpi {
     float *row_max;
     float *row_sum;
     int apply_exp;
+    // fp32 product from three-way bf16 splits (gemm_f32_tc.cu): fp32 output instead of bf16, and
+    // the K loop walks six (segment of A, segment of B) pairs of seg_kb K blocks each.
+    float *c32;
+    int64_t ldc32;
+    int accumulate;
+    int seg_kb;
 };
 
 // max over floats with integer atomics: non-negative values order like signed integers,
@@ -155,8 +161,19 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (!mbar_wait(&empty[s], ph ^ 1, status, 201)) { ok = false; break; }
                     unsigned char *sa = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(sa, &tmap_a, kb * BK, tm * BM, &full[s]);
-                    tma_load_2d(sa + A_BYTES, &tmap_b, kb * BK, tn * BN, &full[s]);
+                    int xa = kb * BK, xb = kb * BK;
+                    if (EPI && epi.seg_kb > 0) {
+                        // a = a1 + a2 + a3, b = b1 + b2 + b3 (bf16 each); the six products that
+                        // matter, smallest first: a3 b1, a2 b2, a1 b3, a2 b1, a1 b2, a1 b1.
+                        // Segment i of an operand starts at column i * seg_kb * BK of its rows.
+                        const int pair = kb / epi.seg_kb, r = kb - pair * epi.seg_kb;
+                        const int seg_a = (0x210100 >> (4 * (5 - pair))) & 15;   // 2 1 0 1 0 0
+                        const int seg_b = (0x012010 >> (4 * (5 - pair))) & 15;   // 0 1 2 0 1 0
+                        xa = (seg_a * epi.seg_kb + r) * BK;
+                        xb = (seg_b * epi.seg_kb + r) * BK;
+                    }
+                    tma_load_2d(sa, &tmap_a, xa, tm * BM, &full[s]);
+                    tma_load_2d(sa + A_BYTES, &tmap_b, xb, tn * BN, &full[s]);
                 }
             }
         }
@@ -235,7 +252,30 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                     }
                 }
-                if (EPI && C == nullptr) {
+                if (EPI && epi.c32 != nullptr) {
+                    if (row < M && col < N) {
+                        float *dst = epi.c32 + static_cast<int64_t>(row) * epi.ldc32 + col;
+                        const bool v4 = (epi.ldc32 % 4 == 0) && ((reinterpret_cast<uintptr_t>(epi.c32) & 15) == 0) &&
+                                        col + 32 <= N;
+                        if (v4) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                float4 o = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                                if (epi.accumulate) {
+                                    const float4 c = *reinterpret_cast<const float4 *>(dst + 4 * q);
+                                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                                }
+                                *reinterpret_cast<float4 *>(dst + 4 * q) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < N)
+                                    dst[j] = __uint_as_float(r[j]) + (epi.accumulate ? dst[j] : 0.0f);
+                        }
+                    }
+                } else if (EPI && C == nullptr) {
                     // reductions only: the product itself is a temporary that is never stored
                 } else if (splits > 1) {
                     // fp32 partial sums into slab `split` of the workspace ([splits][M][N])
@@ -420,6 +460,47 @@ static int launch_tc_plain(gb200_ctx *ctx, const void *A, int64_t lda, const voi
     return after_launch(ctx, "gemm_bf16_tc_kernel");
 }
 
+template <int TILE_N>
+static int launch_tc_f32x3(gb200_ctx *ctx, const void *A3, const void *B3, float *C, int64_t ldc,
+                           int64_t M, int64_t N, int64_t Kp, int accumulate, cudaStream_t stream) {
+    using namespace gemm;
+    constexpr int smem_bytes = STAGES * (A_BYTES + TILE_N * BK * 2) + 1024 + 256;
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(3 * Kp), (uint64_t)M,
+                         (uint64_t)(3 * Kp) * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(3 * Kp), (uint64_t)N,
+                     (uint64_t)(3 * Kp) * 2, BK, TILE_N, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + TILE_N - 1) / TILE_N);
+    const int grid = (int)(n_tiles < ctx->sm_count ? n_tiles : ctx->sm_count);
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_tc_kernel<true, TILE_N>, smem_bytes);
+    if (rc) return rc;
+    GemmEpi epi{};
+    epi.alpha = 1.0f;
+    epi.c32 = C;
+    epi.ldc32 = ldc;
+    epi.accumulate = accumulate;
+    epi.seg_kb = (int)(Kp / BK);
+    // the kernel sees one K loop of 6 * Kp: six segment pairs of Kp each
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_tc_kernel<true, TILE_N>, dim3(grid), dim3(NUM_THREADS),
+                              (size_t)smem_bytes, stream, ta, tb, static_cast<__nv_bfloat16 *>(nullptr),
+                              (int64_t)0, (int)M, (int)N, (int)(6 * Kp), 1, static_cast<float *>(nullptr),
+                              ctx->d_status, epi));
+    return after_launch(ctx, "gemm_bf16_tc_kernel<f32x3>");
+}
+
+// fp32 C (+)= A B from operands already split into three bf16 terms each: A3 is [M][3*Kp], B3 is
+// [N][3*Kp] (both K-contiguous, Kp a multiple of 64, zero-padded).  Used by gemm_f32_tc.cu.
+int gemm_f32x3_launch(gb200_ctx *ctx, const void *A3, const void *B3, float *C, int64_t ldc,
+                      int64_t M, int64_t N, int64_t Kp, int accumulate, cudaStream_t stream) {
+    GB200_REQUIRE(ctx->encode_tiled != nullptr, GB200_ERR_NO_DEVICE, "TMA descriptors unavailable");
+    const int tile_n = pick_tile_n(M, N, ctx->sm_count);
+    if (tile_n == 192) return launch_tc_f32x3<192>(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);
+    if (tile_n == 128) return launch_tc_f32x3<128>(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);
+    return launch_tc_f32x3<256>(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);
+}
+
 // kernel_choice: 0 = pick, 1 = single-CTA 128 x 256 tiles, 2 = CTA-pair tiles, 3 / 4 = single-CTA
 // tiles of 192 / 128 columns.
 int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
@@ -535,7 +616,7 @@ int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const v
     GB200_REQUIRE(A != nullptr && B != nullptr, GB200_ERR_INVALID_ARG, "NULL matrix pointer");
     GB200_REQUIRE(lda >= K && ldb >= K && (C == nullptr || ldc >= N), GB200_ERR_INVALID_ARG,
                   "leading dimension smaller than the row");
-    GemmEpi epi;
+    GemmEpi epi{};
     epi.alpha = e->alpha;
     epi.row_sub = e->row_sub;
     epi.row_div = e->row_div;

@@ -193,9 +193,22 @@ int check_gemm_args(const void *A, int64_t lda, const void *B, int64_t ldb, void
     return GB200_OK;
 }
 
+int gemm_f32_tc_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
+                         float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
+                         cudaStream_t stream);
+
+#ifndef GB200_GEMM_F32_TC_MIN_FLOP
+#define GB200_GEMM_F32_TC_MIN_FLOP 6.0e8   // measured: 512^3 19.0 vs 24.8 us, 768^3 43.6 vs 34.7 us
+#endif
+
+// kernel_choice: 0 = pick, 1 = CUDA cores, 2 = tensor cores (three-way bf16 split).
 int gemm_f32_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
                       float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, int kernel_choice = 0) {
+    const bool tc_ok = ctx->encode_tiled != nullptr && K > 0;
+    const bool tc_pays = 2.0 * (double)M * (double)N * (double)K >= GB200_GEMM_F32_TC_MIN_FLOP;
+    if (tc_ok && (kernel_choice == 2 || (kernel_choice == 0 && tc_pays)))
+        return gemm_f32_tc_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream);
     const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
     if (big_tiles >= 2 * (int64_t)ctx->sm_count) {
         dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128));
@@ -226,6 +239,18 @@ int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, 
     if (rc) return rc < 0 ? rc : GB200_OK;
     return gemm_f32_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate,
                              static_cast<cudaStream_t>(stream));
+}
+
+// Test / benchmark hook: kernel chosen by the caller (1 = CUDA cores, 2 = tensor cores).
+int gb200_gemm_f32_variant(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
+                           float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
+                           void *stream, int variant) {
+    int rc = enter(ctx);
+    if (rc) return rc;
+    rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, false);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return gemm_f32_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate,
+                             static_cast<cudaStream_t>(stream), variant);
 }
 
 int gb200_gemm_f32_host(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,

@@ -62,6 +62,67 @@ def test_f32_shapes(ctx, oracle, mnk):
     assert frob(cg.cpu().numpy(), want - c0) < 1e-5
 
 
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("mnk", [(1, 1, 1), (5, 7, 3), (64, 64, 64), (100, 130, 250), (257, 129, 513), (512, 512, 512),
+                                 (1024, 768, 300)])
+def test_f32_kernel_variants(ctx, oracle, mnk, variant):
+    """CUDA-core kernels (1) and the tensor-core path with three-way bf16 splits (2), forced:
+    both must meet the fp32 bars (|delta| < 1e-3, relative Frobenius error < 1e-5), with and
+    without accumulation into C."""
+    m, n, k = mnk
+    rng = np.random.default_rng(m * 77 + n * 3 + k)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.matmul_tiled(a, b, 64, 64, 64, c0.copy())
+    oracle.set_threads(1)
+    pad = 5   # rows of C not 16-byte aligned, guard columns behind them
+    ag, bg = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    cg = torch.full((m, n + pad), 9.0, device="cuda")
+    cg[:, :n] = torch.from_numpy(c0).cuda()
+    ctx.gemm_f32(ag, bg, cg[:, :n], accumulate=True, variant=variant)
+    ctx.sync()
+    got = cg[:, :n].cpu().numpy()
+    assert bool((cg[:, n:] == 9.0).all()), "wrote past the row"
+    assert np.abs(got - want).max() < 1e-3
+    assert frob(got, want) < 1e-5
+    ctx.gemm_f32(ag, bg, cg[:, :n], accumulate=False, variant=variant)
+    ctx.sync()
+    assert frob(cg[:, :n].cpu().numpy(), want - c0) < 1e-5
+
+
+def test_f32_tensor_core_path_is_exact_on_small_integers(ctx):
+    # the reference's own check: 10 x 10 ascending integers, == (test/test-cpu-mm.cpp:13-83); on the
+    # split path integers below 2^8 are their own first bf16 term, so every product is exact
+    m = n = k = 160
+    a = (torch.arange(m * k, device="cuda") % 13).float().reshape(m, k)
+    b = (torch.arange(k * n, device="cuda") % 7).float().reshape(k, n)
+    c = torch.zeros((m, n), device="cuda")
+    ctx.gemm_f32(a, b, c, variant=2)
+    ctx.sync()
+    assert torch.equal(c, a.double().matmul(b.double()).float())
+
+
+def test_f32_large_goes_to_the_tensor_cores_and_keeps_fp32_accuracy(ctx, oracle):
+    m, n, k = 2048, 1536, 1024          # 6.4 GFLOP: above the switch-over
+    rng = np.random.default_rng(9)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    ag, bg = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    c = torch.zeros((m, n), device="cuda")
+    ctx.gemm_f32(ag, bg, c)
+    ctx.sync()
+    rows = np.arange(0, m, 37)
+    want = a[rows].astype(np.float64) @ b.astype(np.float64)
+    got = c.cpu().numpy()[rows]
+    assert frob(got, want) < 1e-6
+    c1 = torch.zeros((m, n), device="cuda")
+    ctx.gemm_f32(ag, bg, c1, variant=1)
+    ctx.sync()
+    assert frob(c1.cpu().numpy()[rows], want) < 1e-6
+
+
 def test_f32_k_zero_and_empty(ctx):
     c = torch.full((4, 4), 3.0, device="cuda")
     a = torch.zeros((4, 0), device="cuda")
