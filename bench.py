@@ -207,7 +207,7 @@ class BlurWorkload(Workload):
         read = (self.band.band_rows + self.band.halo_rows) * n * 4
         write = self.band.out_rows * self.oc * 4
         if self.world == 1:
-            read = n * n * 4      # the stored image, padding included (the survey's accounting)
+            read = n * n * 4      # the stored image, padding included
         return float(read + write)
 
     def step(self, stream):
