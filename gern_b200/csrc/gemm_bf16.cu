@@ -492,9 +492,16 @@ static int launch_tc_f32x3(gb200_ctx *ctx, const void *A3, const void *B3, float
 
 // fp32 C (+)= A B from operands already split into three bf16 terms each: A3 is [M][3*Kp], B3 is
 // [N][3*Kp] (both K-contiguous, Kp a multiple of 64, zero-padded).  Used by gemm_f32_tc.cu.
+int gemm_f32x3_2cta_launch(gb200_ctx *ctx, const void *A3, const void *B3, float *C, int64_t ldc,
+                           int64_t M, int64_t N, int64_t Kp, int accumulate, cudaStream_t stream);
+
 int gemm_f32x3_launch(gb200_ctx *ctx, const void *A3, const void *B3, float *C, int64_t ldc,
                       int64_t M, int64_t N, int64_t Kp, int accumulate, cudaStream_t stream) {
     GB200_REQUIRE(ctx->encode_tiled != nullptr, GB200_ERR_NO_DEVICE, "TMA descriptors unavailable");
+    // CTA-pair tiles when there are enough of them to fill the SM pairs, as for bf16 operands
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    if (GB200_GEMM_AUTO_PAIR && pair_tiles >= ctx->sm_count / 2)
+        return gemm_f32x3_2cta_launch(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);
     const int tile_n = pick_tile_n(M, N, ctx->sm_count);
     if (tile_n == 192) return launch_tc_f32x3<192>(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);
     if (tile_n == 128) return launch_tc_f32x3<128>(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);

@@ -44,10 +44,20 @@ __device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, in
     tn = r / rows_in_group;
 }
 
+// fp32 output from three-way bf16 splits (gemm_f32_tc.cu): when c32 is set the K loop walks six
+// (segment of A, segment of B) pairs of seg_kb K blocks each and the epilogue stores fp32.
+struct Gemm2F32 {
+    float *c32;
+    int64_t ldc32;
+    int accumulate;
+    int seg_kb;
+};
+
+template <bool F32X3>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::NUM_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
-                      int64_t ldc, int M, int N, int K, int *status) {
+                      int64_t ldc, int M, int N, int K, int *status, Gemm2F32 f32) {
     using namespace gemm2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -109,8 +119,18 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     // the leader's barrier collects the bytes of all four loads of the pair
                     if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
                     const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
-                    tma_load_2d_pair(sa, &tmap_a, kb * BK, tm * BM + (int)rank * HALF, full_leader);
-                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, kb * BK, tn * BN + (int)rank * HALF, full_leader);
+                    int xa = kb * BK, xb = kb * BK;
+                    if (F32X3) {
+                        // a3 b1, a2 b2, a1 b3, a2 b1, a1 b2, a1 b1 (smallest first); segment i of
+                        // an operand starts at column i * seg_kb * BK of its rows
+                        const int sp = kb / f32.seg_kb, r = kb - sp * f32.seg_kb;
+                        const int seg_a = (0x210100 >> (4 * (5 - sp))) & 15;
+                        const int seg_b = (0x012010 >> (4 * (5 - sp))) & 15;
+                        xa = (seg_a * f32.seg_kb + r) * BK;
+                        xb = (seg_b * f32.seg_kb + r) * BK;
+                    }
+                    tma_load_2d_pair(sa, &tmap_a, xa, tm * BM + (int)rank * HALF, full_leader);
+                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, xb, tn * BN + (int)rank * HALF, full_leader);
                 }
             }
         }
@@ -166,7 +186,30 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 tmem_ld_32x32(taddr + ch * 32, r);
                 tmem_ld_wait();
                 const int col = tn * BN + ch * 32;
-                if (row < M && col < N) {
+                if (F32X3) {
+                    if (row < M && col < N) {
+                        float *dst = f32.c32 + static_cast<int64_t>(row) * f32.ldc32 + col;
+                        const bool v4 = (f32.ldc32 % 4 == 0) &&
+                                        ((reinterpret_cast<uintptr_t>(f32.c32) & 15) == 0) && col + 32 <= N;
+                        if (v4) {
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                float4 o = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                       __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                                if (f32.accumulate) {
+                                    const float4 c = *reinterpret_cast<const float4 *>(dst + 4 * q);
+                                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                                }
+                                *reinterpret_cast<float4 *>(dst + 4 * q) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col + j < N)
+                                    dst[j] = __uint_as_float(r[j]) + (f32.accumulate ? dst[j] : 0.0f);
+                        }
+                    }
+                } else if (row < M && col < N) {
                     __nv_bfloat16 *dst = C + static_cast<int64_t>(row) * ldc + col;
                     if (vec32_ok && col + 32 <= N) {
                         // a thread owns 64 contiguous bytes of its row: two full 32-byte sectors
@@ -226,12 +269,40 @@ int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int64_t pairs = ctx->sm_count / 2;
     if (pairs > n_tiles) pairs = n_tiles;
-    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel, SMEM_BYTES);
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<false>, SMEM_BYTES);
     if (rc) return rc;
-    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<false>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                               (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
-                              (int)N, (int)K, ctx->d_status));
+                              (int)N, (int)K, ctx->d_status, Gemm2F32{}));
     return after_launch(ctx, "gemm_bf16_2cta_kernel");
+}
+
+// fp32 C (+)= A B on CTA pairs from operands split into three bf16 terms: A3 [M][3*Kp],
+// B3 [N][3*Kp], K-contiguous, Kp a multiple of 64 (see gemm_f32_tc.cu).
+int gemm_f32x3_2cta_launch(gb200_ctx *ctx, const void *A3, const void *B3, float *C, int64_t ldc,
+                           int64_t M, int64_t N, int64_t Kp, int accumulate, cudaStream_t stream) {
+    using namespace gemm2;
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(3 * Kp), (uint64_t)M,
+                         (uint64_t)(3 * Kp) * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(3 * Kp), (uint64_t)N,
+                     (uint64_t)(3 * Kp) * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int64_t pairs = ctx->sm_count / 2;
+    if (pairs > n_tiles) pairs = n_tiles;
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<true>, SMEM_BYTES);
+    if (rc) return rc;
+    Gemm2F32 f32;
+    f32.c32 = C;
+    f32.ldc32 = ldc;
+    f32.accumulate = accumulate;
+    f32.seg_kb = (int)(Kp / BK);
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<true>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+                              (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(nullptr),
+                              (int64_t)0, (int)M, (int)N, (int)(6 * Kp), ctx->d_status, f32));
+    return after_launch(ctx, "gemm_bf16_2cta_kernel<f32x3>");
 }
 
 }  // namespace gb200

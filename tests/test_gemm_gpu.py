@@ -123,6 +123,24 @@ def test_f32_large_goes_to_the_tensor_cores_and_keeps_fp32_accuracy(ctx, oracle)
     assert frob(c1.cpu().numpy()[rows], want) < 1e-6
 
 
+def test_f32_cta_pair_path(ctx):
+    # 10 x 9 tiles of 256 x 256: enough for the CTA-pair kernel; ragged K, accumulation into C
+    m, n, k = 2560, 2300, 328
+    rng = np.random.default_rng(21)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    ag, bg, cg = (torch.from_numpy(t).cuda() for t in (a, b, c0))
+    ctx.gemm_f32(ag, bg, cg, accumulate=True)
+    ctx.sync()
+    rows = np.arange(0, m, 53)
+    want = a[rows].astype(np.float64) @ b.astype(np.float64) + c0[rows]
+    assert frob(cg.cpu().numpy()[rows], want) < 1e-6
+    ctx.gemm_f32(ag, bg, cg, accumulate=False)
+    ctx.sync()
+    assert frob(cg.cpu().numpy()[rows], want - c0[rows]) < 1e-6
+
+
 def test_f32_k_zero_and_empty(ctx):
     c = torch.full((4, 4), 3.0, device="cuda")
     a = torch.zeros((4, 0), device="cuda")
