@@ -19,6 +19,10 @@
  *   - `_host` entry points take host pointers (pinned memory is fastest), copy the operands
  *     to the device, run the same kernels, copy the result back and return after the result
  *     is in host memory.
+ *   - A context owns one scratch workspace (split-K slabs of the bf16 GEMM, split copies of the
+ *     fp32 matmul's operands) and one set of staging buffers: calls on the same context whose
+ *     kernels could overlap on the GPU (different streams) must use different contexts, as
+ *     Gern's single-stream hooks never overlap (src/codegen/codegen.cpp:576-611).
  *   - Status: 0 = success; negative = failure (see gb200_status).  A human-readable message
  *     for the calling thread's last failure is returned by gb200_last_error_string().
  */
