@@ -105,6 +105,8 @@ int gemm_f32_tc_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const floa
                          float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
                          cudaStream_t stream) {
     const int64_t Kp = (K + 63) / 64 * 64;
+    GB200_REQUIRE(6 * Kp < (1ll << 31) && M < (1ll << 31) && N < (1ll << 31), GB200_ERR_UNSUPPORTED,
+                  "fp32 matmul on the tensor cores: extent beyond 2^31 / 6");
     const size_t a_bytes = (size_t)M * 3 * Kp * 2, b_bytes = (size_t)N * 3 * Kp * 2;
     const size_t a_off = 0, b_off = (a_bytes + 255) / 256 * 256;
     int rc = workspace_reserve(ctx, b_off + b_bytes);
