@@ -178,7 +178,11 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
     // Input rows >= in_rows_local are not in `in`: they are the rows of the next row band and
     // are read from `halo` (which may be a peer GPU's memory; ordinary loads only).
     const int out_cols = in_cols - 2;
-    const int c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
+    // one-dimensional grid (the y extent of a grid stops at 65535 block rows): column blocks
+    // fastest, so that blocks in flight walk the image row-major
+    const int nbx = (out_cols + 511) / 512;
+    const int bx = blockIdx.x % nbx, by_lin = blockIdx.x / nbx, nby = gridDim.x / nbx;
+    const int c0 = (bx * 128 + threadIdx.x) * 4;
     // Launched with programmatic stream serialisation: blocks may become resident while the
     // previous kernel of the stream drains; nothing is read before that kernel has completed.
     pdl_launch_dependents();
@@ -186,7 +190,7 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
     if (c0 >= out_cols) return;
     // With a halo the block rows run bottom-up, so that the few blocks that read the (possibly
     // remote, high-latency) halo rows start first and finish under the rest of the kernel.
-    const int by = halo != nullptr ? (gridDim.y - 1 - blockIdx.y) : blockIdx.y;
+    const int by = halo != nullptr ? (nby - 1 - by_lin) : by_lin;
     const int r_begin = by * ROWS;
     const int n_out = min(ROWS, out_rows - r_begin);
     const int ncol = min(4, out_cols - c0);
@@ -389,7 +393,9 @@ static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
                       int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream,
                       const float *halo = nullptr, int64_t halo_ld = 0) {
     const int64_t out_rows = in_rows - 2, out_cols = in_cols - 2;
-    dim3 grid((unsigned)((out_cols + 511) / 512), (unsigned)((out_rows + ROWS - 1) / ROWS));
+    const int64_t n_blocks = ((out_cols + 511) / 512) * ((out_rows + ROWS - 1) / ROWS);
+    GB200_REQUIRE(n_blocks < (1ll << 31), GB200_ERR_UNSUPPORTED, "blur: more than 2^31 blocks");
+    dim3 grid((unsigned)n_blocks);
     GB200_CUDA_TRY(launch_pdl(blur3x3_reg_kernel<ROWS>, grid, dim3(128), 0, stream, in, in_ld, (int)in_cols,
                               out, out_ld, (int)out_rows, (aligned16(out) && out_ld % 4 == 0) ? 1 : 0,
                               (int)(halo ? in_rows - 2 : in_rows), halo, halo_ld));

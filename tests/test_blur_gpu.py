@@ -52,6 +52,21 @@ def test_padded_leading_dimensions_and_unaligned(ctx, oracle):
     assert np.array_equal(run_blur(ctx, x, None, in_pad=7, out_pad=1), want)   # TMA-eligible input
 
 
+def test_tall_image_beyond_the_grid_y_limit(ctx, oracle):
+    # 300000 output rows: more block rows than a grid's y extent (65535) could index
+    rows, cols = 300002, 70
+    x = np.random.default_rng(5).random((rows, cols), dtype=np.float32)
+    xin = torch.zeros((rows, cols + 2), dtype=torch.float32, device="cuda")
+    xin[:, :cols] = torch.from_numpy(x).cuda()
+    out = torch.empty((rows - 2, cols - 2), dtype=torch.float32, device="cuda")
+    ctx.blur3x3(xin[:, :cols], out)
+    ctx.sync()
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.blur_xy(x)
+    oracle.set_threads(1)
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
 def test_empty_outputs_are_no_ops(ctx):
     for shape in ((0, 0), (2, 100), (100, 2), (1, 1)):
         x = np.zeros(shape, np.float32)
