@@ -60,9 +60,10 @@ __device__ __forceinline__ void store4(float *dst, uint64_t o01, uint64_t o23, i
 // S stages of RS rows x 132 columns (one TMA box: the strip plus the 4 columns to its right)
 // with private mbarriers, so no block-level barrier exists and warps drift freely.  The stencil
 // runs on fp32x2 pairs, the output pointer is carried instead of recomputed, and whole chunks
-// of interior lanes take a branch-free path.  Measured slower on B200 than the register-staged
-// kernel below (long-lived strips spread the DRAM accesses over the whole image), so it is an
-// alternative, not the default.
+// of interior lanes take a branch-free path.  With one wave of long-lived strips it is clearly
+// slower on B200 than the register-staged kernel below (the strips spread the DRAM accesses over
+// the whole image: 105 against 79 us at 8192^2); cut into 16 waves of strips about 10 rows tall it
+// comes within 1.4 % (80.0 us).  It stays an alternative, not the default.
 // ---------------------------------------------------------------------------------------
 template <int RS, int S>
 struct BlurWarpCfg {
@@ -87,6 +88,9 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict
     float *stage = reinterpret_cast<float *>(base) + warp * Cfg::WARP_F;
     uint64_t *full = reinterpret_cast<uint64_t *>(base + Cfg::WARPS * Cfg::WARP_F * 4) + warp * S;
 
+    // launched with launch_pdl: nothing is read before the previous kernel of the stream is done
+    pdl_launch_dependents();
+    pdl_wait();
     const int item = blockIdx.x * Cfg::WARPS + warp;
     if (item >= n_items) return;
     const int strip = item % n_strips;
@@ -381,9 +385,10 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
         const int rc_attr = ensure_dynamic_smem(ctx, kern, Cfg::SMEM_BYTES);
         if (rc_attr) return rc_attr;
     }
-    kern<<<(unsigned)((n_items + Cfg::WARPS - 1) / Cfg::WARPS), 128, Cfg::SMEM_BYTES, stream>>>(
-        tm, out, out_ld, (int)out_rows, (int)out_cols, (int)rows_per_band, n_strips, (int)n_items,
-        (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, ctx->d_status);
+    GB200_CUDA_TRY(launch_pdl(kern, dim3((unsigned)((n_items + Cfg::WARPS - 1) / Cfg::WARPS)), dim3(128),
+                              (size_t)Cfg::SMEM_BYTES, stream, tm, out, out_ld, (int)out_rows, (int)out_cols,
+                              (int)rows_per_band, n_strips, (int)n_items,
+                              (aligned16(out) && out_ld % 4 == 0) ? 1 : 0, ctx->d_status));
     return after_launch(ctx, "blur3x3_tma_kernel");
 }
 
@@ -418,6 +423,8 @@ static int check_blur_args(const float *in, int64_t in_ld, int64_t in_rows, int6
 // variant 0 picks: the register-staged kernel for 16-byte aligned input rows, else the generic
 // kernel.  Other variants exist for the parity tests and for benchmarking:
 //   1 = generic direct kernel,  2 = TMA-staged kernel (one wave),  3 = TMA-staged, 4 waves,
+//   50 + k = TMA-staged, 4 * 2^k waves of ever shorter strips (52: 16 waves, its best: 80.0 us
+//   at 8192^2 against 78.9 us for the register-staged kernel),
 //   40 + k = register-staged kernel with 2, 3, 4, 6, 8 output rows per block (k = 0..4).
 int blur_dispatch(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows, int64_t in_cols,
                   float *out, int64_t out_ld, cudaStream_t stream, int variant) {
@@ -430,6 +437,8 @@ int blur_dispatch(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_row
         return launch_tma<8, 2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream, 1);
     if (variant == 3 && tma_ok)
         return launch_tma<8, 2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream, 4);
+    if (variant >= 50 && variant < 60 && tma_ok)   // 50 + k: 2^k * 4 waves of ever shorter strips
+        return launch_tma<8, 2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream, 4 << (variant - 50));
     switch (variant) {
         case 40: return launch_reg<2>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);
         case 41: return launch_reg<3>(ctx, in, in_ld, in_rows, in_cols, out, out_ld, stream);

@@ -29,7 +29,7 @@ def test_golden_fixtures(ctx, golden):
 
 @pytest.mark.parametrize("shape", [(3, 3), (4, 7), (16, 64), (17, 65), (64, 260), (67, 131), (130, 259),
                                    (300, 1028), (257, 2050), (1024, 1024), (1026, 516)])
-@pytest.mark.parametrize("variant", [None, 1, 2, 3, 40, 44])
+@pytest.mark.parametrize("variant", [None, 1, 2, 3, 40, 44, 52])
 def test_matches_oracle(ctx, oracle, shape, variant):
     x = np.random.default_rng(shape[0] * 7919 + shape[1]).random(shape, dtype=np.float32)
     assert np.array_equal(run_blur(ctx, x, variant), oracle.blur_xy(x))
@@ -40,7 +40,7 @@ def test_aligned_output_rows_take_vector_stores(ctx, oracle, shape):
     # cols - 2 is a multiple of 4: output rows are 16-byte aligned, so the 128-bit store path runs
     x = np.random.default_rng(shape[1]).random(shape, dtype=np.float32)
     want = oracle.blur_xy(x)
-    for variant in (None, 1, 2, 3, 41, 43):
+    for variant in (None, 1, 2, 3, 41, 43, 52):
         assert np.array_equal(run_blur(ctx, x, variant, in_pad=2), want)
     assert np.array_equal(run_blur(ctx, x, None, in_pad=2, out_pad=4), want)
 
