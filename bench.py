@@ -163,6 +163,7 @@ class BlurWorkload(Workload):
     dtype = "f32"
     kernel = "blur3x3_reg_kernel"
     N = 8192
+    VARIANT = None      # --variant: a kernel variant of the library's test hook (N = 1 only)
 
     def __init__(self, ctx, rank, world, torch, dist=None):
         super().__init__(ctx, rank, world, torch)
@@ -215,7 +216,7 @@ class BlurWorkload(Workload):
         n = self.N
         band = self.band
         if self.world == 1:
-            self.ctx.blur3x3(self.x[:, : n - 2], self.out, stream=stream)
+            self.ctx.blur3x3(self.x[:, : n - 2], self.out, stream=stream, variant=self.VARIANT)
             return
         if self.mode.startswith("NCCL"):
             self.side.wait_stream(torch.cuda.current_stream())
@@ -661,6 +662,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--small", action="store_true",
                     help="reduced sizes (still larger than L2) for profiler captures; not a bench number")
+    ap.add_argument("--variant", type=int, default=None,
+                    help="blur only, one GPU: kernel variant of gb200_blur3x3_f32_variant (52 = TMA-staged, short strips)")
     ap.add_argument("--shape", default="", help="gemm_bf16 / gemm_f32: M,N,K of a side measurement (kernel only)")
     ap.add_argument("--vs-cublas", action="store_true",
                     help="with --shape: add cuBLAS (torch.matmul) timed the same way under 'library'")
@@ -693,6 +696,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.variant is not None:
+        BlurWorkload.VARIANT = args.variant
+        if 2 <= args.variant < 40 or args.variant >= 50:
+            BlurWorkload.kernel = "blur3x3_tma_kernel"
     if args.shape:
         GemmBf16Workload.SHAPE = tuple(int(v) for v in args.shape.split(","))
         GemmF32ShapeWorkload.SHAPE = GemmBf16Workload.SHAPE
