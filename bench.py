@@ -811,7 +811,7 @@ def main():
     if world == 1 and args.also:
         for name in [s for s in args.also.split(",") if s in WORKLOADS and s != args.workload]:
             try:
-                r = run_workload(name, min(args.steps, 10), 3, False, False)
+                r = run_workload(name, min(args.steps, 20), 5, False, False)
                 also[name] = {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
                               "frac_of_peak": r["roofline"]["frac"], "bound": r["roofline"]["bound"]}
             except Exception as e:  # a failing side workload must not hide the headline line
