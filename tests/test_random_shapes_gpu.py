@@ -56,6 +56,7 @@ def test_softmax(ctx, many_threads):
 
 def test_gemm_bf16(ctx, many_threads):
     rng = np.random.default_rng(103)
+    torch.manual_seed(103)
     for i in range(30):
         m, n, k = int(rng.integers(1, 700)), int(rng.integers(1, 900)), int(rng.integers(1, 600))
         k_alloc = (k + 7) // 8 * 8 if i % 3 else k      # every third case: rows not 16-byte aligned
@@ -85,6 +86,7 @@ def test_gemm_f32(ctx):
 
 def test_attention(ctx, many_threads):
     rng = np.random.default_rng(105)
+    torch.manual_seed(105)
     for i in range(18):
         nq, nkv = int(rng.integers(1, 700)), int(rng.integers(1, 1500))
         q = torch.randn((nq, 128), device="cuda").to(torch.bfloat16)
