@@ -71,32 +71,40 @@ split_rows_kernel(const float *__restrict__ A, int64_t ld, int rows, int cols, i
 }
 
 // B [K][N] fp32 row-major (ld) -> out [N][3 * Kp] bf16 (transposed, so that K is contiguous),
-// through a 32 x 32 shared-memory tile; rows K..Kp-1 of B count as zero.
+// through a 64 (k) x 32 (n) shared-memory tile: rows of B are read 128 bytes per warp, and each
+// thread writes 8 adjacent k of one n as three 16-byte stores.  Rows K..Kp-1 of B count as zero.
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float *__restrict__ B, int64_t ld, int K, int N, int Kp,
                        __nv_bfloat16 *__restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float tile[32][33];
+    __shared__ float tile[64][33];
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
-    const int k0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    const int k0 = blockIdx.y * 64, n0 = blockIdx.x * 32;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
         const int k = k0 + ty + 8 * i, n = n0 + tx;
         tile[ty + 8 * i][tx] = (k < K && n < N) ? B[static_cast<int64_t>(k) * ld + n] : 0.0f;
     }
     __syncthreads();
+    const int nl = threadIdx.x >> 3, kg = (threadIdx.x & 7) * 8;   // this thread: row n0 + nl, k0 + kg ..+7
+    const int n = n0 + nl;
+    if (n < N) {
+        uint32_t w[3][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int n = n0 + ty + 8 * i, k = k0 + tx;
-        if (n < N && k < Kp) {
-            __nv_bfloat16 h1, h2, h3;
-            split3(tile[tx][ty + 8 * i], h1, h2, h3);
-            __nv_bfloat16 *o = out + static_cast<int64_t>(n) * (3ll * Kp) + k;
-            o[0] = h1;
-            o[Kp] = h2;
-            o[2ll * Kp] = h3;
+        for (int j = 0; j < 4; ++j) {
+            __nv_bfloat16 a1, a2, a3, b1, b2, b3;
+            split3(tile[kg + 2 * j][nl], a1, a2, a3);
+            split3(tile[kg + 2 * j + 1][nl], b1, b2, b3);
+            w[0][j] = __bfloat16_as_ushort(a1) | (static_cast<uint32_t>(__bfloat16_as_ushort(b1)) << 16);
+            w[1][j] = __bfloat16_as_ushort(a2) | (static_cast<uint32_t>(__bfloat16_as_ushort(b2)) << 16);
+            w[2][j] = __bfloat16_as_ushort(a3) | (static_cast<uint32_t>(__bfloat16_as_ushort(b3)) << 16);
         }
+        __nv_bfloat16 *o = out + static_cast<int64_t>(n) * (3ll * Kp) + k0 + kg;   // 16-byte aligned
+#pragma unroll
+        for (int sgm = 0; sgm < 3; ++sgm)
+            *reinterpret_cast<uint4 *>(o + static_cast<int64_t>(sgm) * Kp) =
+                make_uint4(w[sgm][0], w[sgm][1], w[sgm][2], w[sgm][3]);
     }
 }
 
@@ -119,7 +127,7 @@ int gemm_f32_tc_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const floa
                               (int)K, (int)Kp, A3));
     rc = after_launch(ctx, "split_rows_kernel");
     if (rc) return rc;
-    dim3 grid((unsigned)((N + 31) / 32), (unsigned)(Kp / 32));
+    dim3 grid((unsigned)((N + 31) / 32), (unsigned)(Kp / 64));
     GB200_CUDA_TRY(launch_pdl(split_transpose_kernel, grid, dim3(256), 0, stream, B, ldb, (int)K, (int)N,
                               (int)Kp, B3));
     rc = after_launch(ctx, "split_transpose_kernel");
