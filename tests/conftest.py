@@ -39,6 +39,17 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def golden_maker():
+    """tests/golden/make_golden.py as a module: the tests regenerate the operands of the bf16
+    fixtures with its bf16_inputs() instead of storing them."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(ROOT, "tests", "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.fixture(scope="session")
 def ctx():
     """The library context on cuda:0.  The shared library must already be built in-tree; there is
     no fallback."""

@@ -254,11 +254,33 @@ def test_bf16_structured_exact(ctx):
     assert torch.equal(c, want)
 
 
+def test_bf16_against_reference_leaf_fixture(ctx, golden, golden_maker):
+    """The CUDA kernels against gern::impl::matrix_multiply (test/library/matrix/impl/cpu-matrix.h:196-212)
+    run by the reference itself on the same bf16-rounded operands (tests/golden/make_golden.py)."""
+    for tag, variants in (("gemm96", (None, 1, 4)), ("gemm512", (None, 1, 2))):
+        a_bits, b_bits = golden_maker.bf16_inputs(tag)
+        a = torch.from_numpy(a_bits.view(np.int16)).cuda().view(torch.bfloat16)
+        b = torch.from_numpy(b_bits.view(np.int16)).cuda().view(torch.bfloat16)
+        for variant in variants:
+            c = torch.zeros((a.shape[0], b.shape[0]), dtype=torch.bfloat16, device="cuda")
+            ctx.gemm_bf16(a, b, c, variant=variant)
+            ctx.sync()
+            got = c.float().cpu().numpy()
+            if tag == "gemm96":
+                want = golden["gemmbf96_c"]
+            else:
+                got, want = got[::8, ::8], golden["gemmbf512_sub"]
+            # fp32 reassociation inside the tensor core plus the final bf16 rounding (2^-9 relative)
+            assert frob(got, want) <= 3e-3, (tag, variant)
+
+
 def test_bf16_full_size_sampled(ctx, oracle):
     """8192^3 (the benchmark size): sampled rows against the oracle, plus linearity A(2B) = 2(AB)."""
     n = 8192
     a, b, c = run_bf16(ctx, n, n, n, seed=0)
-    rows = [0, 1, 127, 128, 4095, 8191]
+    # one row in every 128-row block (both halves of every 256-row CTA-pair tile), at a lane that
+    # moves through the block, plus the corners
+    rows = sorted({0, 1, 127, 128, 4095, 8191} | {blk * 128 + (blk * 37) % 128 for blk in range(n // 128)})
     a_s = np.ascontiguousarray(bits(a[rows].contiguous()))
     oracle.set_threads(oracle.max_threads())
     want = oracle.gemm_bf16(a_s, np.ascontiguousarray(bits(b.contiguous())))

@@ -98,6 +98,29 @@ def test_bf16_helpers_and_gemm_attention_against_fp64(oracle):
     assert np.linalg.norm(o - want) / np.linalg.norm(want) < 1e-5
 
 
+def test_gemm_bf16_matches_reference_leaf_fixture(oracle, golden, golden_maker):
+    # The fixtures hold gern::impl::matrix_multiply (cpu-matrix.h:196-212) on the bf16-rounded
+    # operands widened to fp32: same ascending-k fp32 accumulation, so equality is exact.
+    a, b = golden_maker.bf16_inputs("gemm96")
+    assert np.array_equal(oracle.gemm_bf16(a, b), golden["gemmbf96_c"])
+    a, b = golden_maker.bf16_inputs("gemm512")
+    oracle.set_threads(oracle.max_threads())
+    c = oracle.gemm_bf16(a, b)
+    oracle.set_threads(1)
+    assert np.array_equal(c[::8, ::8], golden["gemmbf512_sub"])
+    assert c.astype(np.float64).sum() == float(golden["gemmbf512_sum"])
+
+
+def test_attention_matches_reference_chain_fixture(oracle, golden, golden_maker):
+    # matrix_multiply -> max_row -> subtract_vec -> exp_matrix -> sum_row -> divide_vec ->
+    # matrix_multiply of the reference's CPU library on the same bf16-rounded Q, K, V.  The
+    # restatement performs the same fp32 operations in the same order (the power-of-two scale
+    # commutes with the rounding of the first product), so the bound is zero.
+    q, k, v = golden_maker.bf16_inputs("attn")
+    o = oracle.attention_bf16(q, k, v, golden_maker.ATTN_SCALE)
+    assert np.array_equal(o, golden["attn_o"])
+
+
 @pytest.mark.skipif(not pyoracle.Reference.available(), reason="oracle/_ref not built (no reference tree)")
 class TestAgainstCompiledReference:
     """Bit-equality between the restatement and the reference's own compiled functions."""
@@ -131,6 +154,15 @@ class TestAgainstCompiledReference:
         v = ref.max_row(x)
         assert np.array_equal(oracle.subtract_vec_ref(v, x), ref.subtract_vec(v, x))
         assert np.array_equal(oracle.divide_vec(v, x), ref.divide_vec(v, x))
+
+    def test_bf16_gemm_and_chain(self, oracle, golden_maker):
+        # what make_golden.py records, recomputed live and compared with the restatement
+        ref = pyoracle.Reference()
+        fx = golden_maker.reference_bf16_fixtures(ref)
+        a, b = golden_maker.bf16_inputs("gemm96")
+        assert np.array_equal(oracle.gemm_bf16(a, b), fx["gemmbf96_c"])
+        q, k, v = golden_maker.bf16_inputs("attn")
+        assert np.array_equal(oracle.attention_bf16(q, k, v, golden_maker.ATTN_SCALE), fx["attn_o"])
 
     def test_random_fill(self):
         ref = pyoracle.Reference()
