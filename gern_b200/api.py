@@ -61,6 +61,9 @@ lib.gb200_launch_count.argtypes = [_vp]
 lib.gb200_launch_count.restype = _i64
 lib.gb200_gemm_bf16_splitk_static.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]
 lib.gb200_gemm_bf16_splitk_static.restype = _int
+lib.gb200_static_status.argtypes = [ctypes.POINTER(_int)]
+lib.gb200_static_status.restype = _int
+SIGNATURES["gb200_static_status"] = None
 
 
 class GemmEpilogue(ctypes.Structure):
@@ -138,6 +141,12 @@ def gemm_bf16_splitk_static(A, Bt, C, splits=0, stream=None):
     N = Bt.shape[0]
     _check(lib.gb200_gemm_bf16_splitk_static(_ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C), _ld(C), M, N, K,
                                              int(splits), _stream(stream)), "gb200_gemm_bf16_splitk_static")
+
+
+def static_status():
+    """gb200_static_status: raises GernB200Error(-5) if a kernel of the static entry gave up a wait."""
+    code = _int(0)
+    _check(lib.gb200_static_status(ctypes.byref(code)), "gb200_static_status")
 
 
 def _shard_array(parts):

@@ -491,8 +491,12 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
 
 static int check_attention_args(const void *Q, int64_t ldq, const void *K, int64_t ldk,
                                 const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
-                                int64_t nkv, int64_t d) {
+                                int64_t nkv, int64_t d, float scale) {
     GB200_REQUIRE(nq >= 0 && nkv >= 0 && d >= 0, GB200_ERR_INVALID_ARG, "negative extent");
+    // The kernels take the row maximum of the raw scores and scale it afterwards, which is the
+    // maximum of the scaled scores only for a positive scale.
+    GB200_REQUIRE(scale > 0.0f && scale <= 3.0e38f, GB200_ERR_INVALID_ARG,
+                  "scale must be positive and finite (got %g)", (double)scale);
     GB200_REQUIRE(nq < (1ll << 30) && nkv < (1ll << 30), GB200_ERR_UNSUPPORTED, "extent beyond 2^30");
     if (nq == 0 || d == 0) return 1;
     GB200_REQUIRE(nkv > 0, GB200_ERR_INVALID_ARG, "softmax over an empty row (nkv == 0)");
@@ -511,9 +515,10 @@ extern "C" {
 int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                          int64_t nkv, int64_t d, float scale, void *stream) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
-    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d);
+    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
     if (rc) return rc < 0 ? rc : GB200_OK;
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
                               static_cast<cudaStream_t>(stream));
@@ -530,9 +535,10 @@ int gb200_attention_bf16_variant(gb200_ctx *ctx, const void *Q, int64_t ldq, con
                                  int64_t ldk, const void *V, int64_t ldv, void *O, int64_t ldo,
                                  int64_t nq, int64_t nkv, int64_t d, float scale, void *stream,
                                  int variant) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
-    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d);
+    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
     if (rc) return rc < 0 ? rc : GB200_OK;
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
                               static_cast<cudaStream_t>(stream), variant);
@@ -541,9 +547,10 @@ int gb200_attention_bf16_variant(gb200_ctx *ctx, const void *Q, int64_t ldq, con
 int gb200_attention_bf16_host(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K,
                               int64_t ldk, const void *V, int64_t ldv, void *O, int64_t ldo,
                               int64_t nq, int64_t nkv, int64_t d, float scale) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
-    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d);
+    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
     if (rc) return rc < 0 ? rc : GB200_OK;
     rc = stage_reserve(ctx, 0, (size_t)nq * d * 2 + 16);
     if (rc) return rc;
@@ -561,8 +568,7 @@ int gb200_attention_bf16_host(gb200_ctx *ctx, const void *Q, int64_t ldq, const 
                             nq, nkv, d, scale, s);
     if (rc) return rc;
     GB200_CUDA_TRY(cudaMemcpy2DAsync(O, ldo * 2, ctx->stage[3], d * 2, d * 2, nq, cudaMemcpyDeviceToHost, s));
-    GB200_CUDA_TRY(cudaStreamSynchronize(s));
-    return GB200_OK;
+    return host_finish(ctx, s, nullptr);
 }
 
 }  // extern "C"

@@ -3,11 +3,16 @@
 //   t(i,j)   = (in(i,j) + in(i,j+1) + in(i,j+2)) / 3        (apps/common/impl/impl.h:190-214)
 //   out(i,j) = (t(i,j)  + t(i+1,j)  + t(i+2,j))  / 3        (apps/common/impl/impl.h:216-250)
 //
-// Both stages run in one kernel and the intermediate `t` lives in registers only.  The
-// reference's emitted kernel (apps/blur/blur.cu:19-45) gathers a 6x12 patch per thread
-// straight from global memory; here a CTA owns a column strip of the image, walks down it, and
-// receives the input through a ring of TMA tiles in shared memory, so every input element is
-// fetched from HBM once per strip and read from shared memory once.
+// Both stages run in one kernel and the intermediate `t` never reaches memory.  The reference's
+// emitted kernel (apps/blur/blur.cu:19-45) gathers a 6x12 patch per thread straight from global
+// memory.  Three kernels here:
+//   blur3x3_reg_kernel    (default) short-lived blocks of 512 columns x ROWS output rows; a thread
+//                         loads its patch with 128-bit and 64-bit loads and keeps both passes in
+//                         registers; the 2-row overlap between vertical neighbours is an L2 hit;
+//                         its band form reads two halo rows through a second pointer.
+//   blur3x3_tma_kernel    (variant) a warp owns a column strip, walks down it and receives the
+//                         input through a ring of TMA tiles in shared memory.
+//   blur3x3_direct_kernel (generic) any alignment and leading dimension.
 //
 // Arithmetic: the association (a+b+c) and a correctly rounded division by 3 are kept, so the
 // result equals the reference's CPU loops (apps/blur/blur.cpp:11-25) under `==` for every finite
@@ -336,6 +341,8 @@ static int launch_direct(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t
                          int64_t out_ld, int64_t row_begin, int64_t row_end, cudaStream_t stream,
                          int rows_per_thread = 32, bool stcs = false) {
     if (row_end <= row_begin) return GB200_OK;
+    // row strips sit in grid.y (at most 65535): taller images get taller strips
+    while ((row_end - row_begin + rows_per_thread - 1) / rows_per_thread > kMaxGridY) rows_per_thread *= 2;
     const int64_t out_cols = in_cols - 2;
     const bool vec = aligned16(in) && aligned16(out) && in_ld % 4 == 0 && out_ld % 4 == 0 &&
                      (halo == nullptr || (aligned16(halo) && halo_ld % 4 == 0));
@@ -456,7 +463,8 @@ extern "C" {
 
 int gb200_blur3x3_f32(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
                       int64_t in_cols, float *out, int64_t out_ld, void *stream) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_blur_args(in, in_ld, in_rows, in_cols, out, out_ld);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -468,7 +476,8 @@ int gb200_blur3x3_f32(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
 int gb200_blur3x3_f32_variant(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
                               int64_t in_cols, float *out, int64_t out_ld, void *stream,
                               int variant) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_blur_args(in, in_ld, in_rows, in_cols, out, out_ld);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -479,7 +488,8 @@ int gb200_blur3x3_f32_variant(gb200_ctx *ctx, const float *in, int64_t in_ld, in
 int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t band_rows,
                            int64_t in_cols, const float *halo, int64_t halo_ld, float *out,
                            int64_t out_ld, void *stream_) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (halo == nullptr)
@@ -498,7 +508,8 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
 
 int gb200_blur3x3_f32_host(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
                            int64_t in_cols, float *out, int64_t out_ld) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_blur_args(in, in_ld, in_rows, in_cols, out, out_ld);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -556,9 +567,7 @@ int gb200_blur3x3_f32_host(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
                                              cudaMemcpyDeviceToHost, down));
         }
     }
-    GB200_CUDA_TRY(cudaStreamSynchronize(up));
-    GB200_CUDA_TRY(cudaStreamSynchronize(down));
-    return GB200_OK;
+    return host_finish(ctx, down, up);
 }
 
 }  // extern "C"

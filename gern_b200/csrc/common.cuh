@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <list>
 #include <map>
 #include <set>
 #include <mutex>
@@ -67,11 +68,19 @@ struct gb200_ctx {
     size_t smem_optin = 0;
     int64_t launches = 0;
     gb200::EncodeTiledFn encode_tiled = nullptr;
-    std::map<gb200::TmapKey, CUtensorMap> tmaps;
+    // Tensor-map cache, least recently used first in `tmap_order`; bounded (kTmapCacheEntries) so
+    // that a caller who passes fresh buffers on every call cannot grow it without limit.
+    struct TmapEntry {
+        CUtensorMap map;
+        std::list<gb200::TmapKey>::iterator pos;
+    };
+    std::map<gb200::TmapKey, TmapEntry> tmaps;
+    std::list<gb200::TmapKey> tmap_order;
     std::set<const void *> smem_attr_done;   // kernels whose dynamic shared memory limit is raised
     std::mutex mu;
     // device status word written by kernels whose bounded waits ran out
     int *d_status = nullptr;
+    int *h_status = nullptr;   // pinned landing place for d_status in the _host entry points
     // staging of the _host entry points (grown on demand, freed at destroy)
     void *stage[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t stage_bytes[4] = {0, 0, 0, 0};
@@ -90,8 +99,22 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
                 uint64_t d0, uint64_t d1, uint64_t stride1_bytes, uint32_t b0, uint32_t b1,
                 CUtensorMapSwizzle swizzle, CUtensorMap *out);
 
+constexpr size_t kTmapCacheEntries = 512;
+constexpr int kMaxGridY = 65535;   // CUDA's limit on gridDim.y and gridDim.z
+
 // Sets the device for the calling thread, as every entry point must before touching CUDA.
 int enter(gb200_ctx *ctx);
+// The same for the extent of one entry point: makes the context's device current and puts the
+// caller's device back when the entry point returns, so that a call on one context does not
+// change what a later context-free call (or the caller's own CUDA code) runs on.
+struct DeviceScope {
+    int saved = -1;
+    int enter(gb200_ctx *ctx);
+    ~DeviceScope();
+};
+// End of a _host entry point: waits for the given streams (s1 may be NULL), then reads the
+// context's status word and reports a bounded wait that ran out as GB200_ERR_TIMEOUT.
+int host_finish(gb200_ctx *ctx, cudaStream_t s0, cudaStream_t s1);
 // Raises a kernel's dynamic shared memory limit once per context (the attribute call costs a
 // microsecond of host time, which a loop of short launches would pay every iteration).
 template <typename Kernel>

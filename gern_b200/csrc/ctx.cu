@@ -24,6 +24,36 @@ int enter(gb200_ctx *ctx) {
     return GB200_OK;
 }
 
+int DeviceScope::enter(gb200_ctx *ctx) {
+    GB200_REQUIRE(ctx != nullptr, GB200_ERR_INVALID_ARG, "ctx is NULL");
+    int cur = -1;
+    GB200_CUDA_TRY(cudaGetDevice(&cur));
+    if (cur != ctx->device) {
+        GB200_CUDA_TRY(cudaSetDevice(ctx->device));
+        saved = cur;
+    }
+    return GB200_OK;
+}
+
+DeviceScope::~DeviceScope() {
+    if (saved >= 0) cudaSetDevice(saved);
+}
+
+int host_finish(gb200_ctx *ctx, cudaStream_t s0, cudaStream_t s1) {
+    if (s1) GB200_CUDA_TRY(cudaStreamSynchronize(s1));
+    // the status word travels behind the last of the work on s0
+    GB200_CUDA_TRY(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, s0));
+    GB200_CUDA_TRY(cudaStreamSynchronize(s0));
+    if (*ctx->h_status != 0) {
+        const int st = *ctx->h_status;
+        cudaMemsetAsync(ctx->d_status, 0, sizeof(int), s0);
+        cudaStreamSynchronize(s0);
+        set_error("a kernel gave up a bounded wait (status code %d); the result is not valid", st);
+        return GB200_ERR_TIMEOUT;
+    }
+    return GB200_OK;
+}
+
 int after_launch(gb200_ctx *ctx, const char *what) {
     cudaError_t err = cudaPeekAtLastError();
     if (err != cudaSuccess) {
@@ -73,7 +103,8 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
     std::lock_guard<std::mutex> lock(ctx->mu);
     auto it = ctx->tmaps.find(key);
     if (it != ctx->tmaps.end()) {
-        *out = it->second;
+        ctx->tmap_order.splice(ctx->tmap_order.end(), ctx->tmap_order, it->second.pos);
+        *out = it->second.map;
         return GB200_OK;
     }
     CUtensorMap tm;
@@ -90,8 +121,12 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
                   (int)rc, (unsigned long long)d0, (unsigned long long)d1, b0, b1);
         return GB200_ERR_CUDA;
     }
-    if (ctx->tmaps.size() > 4096) ctx->tmaps.clear();
-    ctx->tmaps[key] = tm;
+    while (ctx->tmaps.size() >= kTmapCacheEntries) {       // evict the least recently used
+        ctx->tmaps.erase(ctx->tmap_order.front());
+        ctx->tmap_order.pop_front();
+    }
+    ctx->tmap_order.push_back(key);
+    ctx->tmaps[key] = gb200_ctx::TmapEntry{tm, std::prev(ctx->tmap_order.end())};
     *out = tm;
     return GB200_OK;
 }
@@ -119,6 +154,11 @@ int gb200_ctx_create(int device, gb200_ctx **out) {
     }
     GB200_REQUIRE(device >= 0 && device < count, GB200_ERR_INVALID_ARG,
                   "device %d out of range (have %d)", device, count);
+    struct Restore {   // the caller's current device is put back on every return path
+        int saved = -1;
+        ~Restore() { if (saved >= 0) cudaSetDevice(saved); }
+    } restore;
+    if (cudaGetDevice(&restore.saved) != cudaSuccess) { cudaGetLastError(); restore.saved = -1; }
     GB200_CUDA_TRY(cudaSetDevice(device));
     cudaDeviceProp prop;
     GB200_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
@@ -140,6 +180,8 @@ int gb200_ctx_create(int device, gb200_ctx **out) {
         cudaGetLastError();
     err = cudaMalloc(&ctx->d_status, sizeof(int));
     if (err == cudaSuccess) err = cudaMemset(ctx->d_status, 0, sizeof(int));
+    if (err == cudaSuccess) err = cudaMallocHost(&ctx->h_status, sizeof(int));
+    if (err == cudaSuccess) *ctx->h_status = 0;
     for (int i = 0; i < 2 && err == cudaSuccess; ++i)
         err = cudaStreamCreateWithFlags(&ctx->copy_stream[i], cudaStreamNonBlocking);
     for (int i = 0; i < 4 && err == cudaSuccess; ++i)
@@ -155,7 +197,8 @@ int gb200_ctx_create(int device, gb200_ctx **out) {
 
 int gb200_ctx_destroy(gb200_ctx *ctx) {
     if (!ctx) return GB200_OK;
-    cudaSetDevice(ctx->device);
+    DeviceScope scope;
+    if (scope.enter(ctx) != GB200_OK) return GB200_ERR_CUDA;
     cudaDeviceSynchronize();
     for (int i = 0; i < 4; ++i)
         if (ctx->stage[i]) cudaFree(ctx->stage[i]);
@@ -165,12 +208,14 @@ int gb200_ctx_destroy(gb200_ctx *ctx) {
         if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
     delete ctx;
     return GB200_OK;
 }
 
 int gb200_device_sync(gb200_ctx *ctx) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     GB200_CUDA_TRY(cudaDeviceSynchronize());
     int st = 0;

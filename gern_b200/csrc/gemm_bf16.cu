@@ -518,11 +518,18 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     const bool tc_ok = ctx->encode_tiled && al16(A) && al16(B) && lda % 8 == 0 && ldb % 8 == 0 &&
                        K > 0;
     if (!tc_ok) {
-        dim3 grid((unsigned)((N + 15) / 16), (unsigned)((M + 15) / 16));
-        gemm_bf16_simple_kernel<<<grid, 256, 0, stream>>>(
-            static_cast<const __nv_bfloat16 *>(A), lda, static_cast<const __nv_bfloat16 *>(B), ldb,
-            static_cast<__nv_bfloat16 *>(C), ldc, (int)M, (int)N, (int)K);
-        return after_launch(ctx, "gemm_bf16_simple_kernel");
+        // row blocks sit in grid.y (at most 65535): taller problems go out as several row panels
+        const int64_t panel = (int64_t)kMaxGridY * 16;
+        for (int64_t m0 = 0; m0 < M; m0 += panel) {
+            const int64_t mp = M - m0 < panel ? M - m0 : panel;
+            dim3 grid((unsigned)((N + 15) / 16), (unsigned)((mp + 15) / 16));
+            gemm_bf16_simple_kernel<<<grid, 256, 0, stream>>>(
+                static_cast<const __nv_bfloat16 *>(A) + m0 * lda, lda, static_cast<const __nv_bfloat16 *>(B), ldb,
+                static_cast<__nv_bfloat16 *>(C) + m0 * ldc, ldc, (int)mp, (int)N, (int)K);
+            int rc0 = after_launch(ctx, "gemm_bf16_simple_kernel");
+            if (rc0) return rc0;
+        }
+        return GB200_OK;
     }
     CUtensorMap ta, tb;
     int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
@@ -610,7 +617,8 @@ extern "C" {
 int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                              void *C, int64_t ldc, int64_t M, int64_t N, int64_t K,
                              const gb200_gemm_epilogue *e, void *stream) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     GB200_REQUIRE(e != nullptr, GB200_ERR_INVALID_ARG, "epilogue description is NULL");
     GB200_REQUIRE(C != nullptr || e->row_max != nullptr || e->row_sum != nullptr, GB200_ERR_INVALID_ARG,
@@ -636,7 +644,8 @@ int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const v
 
 int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                     void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -649,7 +658,8 @@ int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, i
 int gb200_gemm_bf16_splitk(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                            void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream,
                            int splits) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -744,6 +754,18 @@ int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int
                   "operands need 16-byte aligned bases and pitches (TMA)");
     int device = 0;
     GB200_CUDA_TRY(cudaGetDevice(&device));
+    // The kernels run on the current device: operands in host memory or on another GPU would be
+    // read through addresses that mean nothing there.  The query is host-only and allocates nothing.
+    const void *operands[3] = {A, B, C};
+    for (int i = 0; i < 3; ++i) {
+        cudaPointerAttributes attr;
+        GB200_CUDA_TRY(cudaPointerGetAttributes(&attr, operands[i]));
+        GB200_REQUIRE((attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) &&
+                          (attr.type == cudaMemoryTypeManaged || attr.device == device),
+                      GB200_ERR_INVALID_ARG,
+                      "operand %c is not device memory of the current device %d (memory type %d, device %d)",
+                      "ABC"[i], device, (int)attr.type, attr.device);
+    }
     StaticDeviceState *st = nullptr;
     rc = static_setup(device, &st);
     if (rc) return rc;
@@ -782,11 +804,33 @@ int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int
     return GB200_OK;
 }
 
+// Reports whether a kernel of gb200_gemm_bf16_splitk_static gave up a bounded wait on the current
+// device since the last query.  Synchronises the device (the word is read after everything
+// enqueued so far), clears the word, allocates nothing.
+int gb200_static_status(int *code) {
+    if (code) *code = 0;
+    int device = 0;
+    GB200_CUDA_TRY(cudaGetDevice(&device));
+    StaticDeviceState *st = nullptr;
+    int rc = static_setup(device, &st);
+    if (rc) return rc;
+    GB200_CUDA_TRY(cudaDeviceSynchronize());
+    int word = 0;
+    GB200_CUDA_TRY(cudaMemcpy(&word, st->status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (word == 0) return GB200_OK;
+    GB200_CUDA_TRY(cudaMemset(st->status, 0, sizeof(int)));
+    if (code) *code = word;
+    set_error("a kernel of gb200_gemm_bf16_splitk_static gave up a bounded wait (status code %d); "
+              "products computed since the last query are not valid", word);
+    return GB200_ERR_TIMEOUT;
+}
+
 // Test / benchmark hook: kernel chosen by the caller (1 = single-CTA tiles, 2 = CTA-pair tiles).
 int gb200_gemm_bf16_variant(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                             void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream,
                             int variant) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -796,7 +840,8 @@ int gb200_gemm_bf16_variant(gb200_ctx *ctx, const void *A, int64_t lda, const vo
 
 int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -818,8 +863,7 @@ int gb200_gemm_bf16_host(gb200_ctx *ctx, const void *A, int64_t lda, const void 
     if (rc) return rc;
     GB200_CUDA_TRY(cudaMemcpy2DAsync(C, ldc * 2, ctx->stage[2], dn * 2, N * 2, M,
                                      cudaMemcpyDeviceToHost, s));
-    GB200_CUDA_TRY(cudaStreamSynchronize(s));
-    return GB200_OK;
+    return host_finish(ctx, s, nullptr);
 }
 
 }  // extern "C"

@@ -210,18 +210,30 @@ int gemm_f32_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const float *
     if (tc_ok && (kernel_choice == 2 || (kernel_choice == 0 && tc_pays)))
         return gemm_f32_tc_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream);
     const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
-    if (big_tiles >= 2 * (int64_t)ctx->sm_count) {
-        dim3 grid((unsigned)((N + 127) / 128), (unsigned)((M + 127) / 128));
-        gemm_f32_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, stream>>>(A, lda, B, ldb, C, ldc, (int)M,
-                                                                      (int)N, (int)K, accumulate);
-    } else {
-        dim3 grid((unsigned)((N + 31) / 32), (unsigned)((M + 31) / 32));
-        const int vec_ok = (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
-                           (reinterpret_cast<uintptr_t>(B) & 15) == 0 && lda % 4 == 0 && ldb % 4 == 0;
-        gemm_f32_warpk_kernel<<<grid, 128, 0, stream>>>(A, lda, B, ldb, C, ldc, (int)M, (int)N,
-                                                       (int)K, accumulate, vec_ok);
+    const bool big = big_tiles >= 2 * (int64_t)ctx->sm_count;
+    const int bm = big ? 128 : 32;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(B) & 15) == 0 && lda % 4 == 0 && ldb % 4 == 0;
+    // Row blocks sit in grid.y (at most 65535): a taller problem goes out as several launches over
+    // consecutive row panels, which are independent.
+    const int64_t panel = (int64_t)kMaxGridY * bm;
+    for (int64_t m0 = 0; m0 < M; m0 += panel) {
+        const int64_t mp = M - m0 < panel ? M - m0 : panel;
+        const float *Ap = A + m0 * lda;
+        float *Cp = C + m0 * ldc;
+        if (big) {
+            dim3 grid((unsigned)((N + 127) / 128), (unsigned)((mp + 127) / 128));
+            gemm_f32_kernel<128, 128, 16, 8, 8><<<grid, 256, 0, stream>>>(Ap, lda, B, ldb, Cp, ldc, (int)mp,
+                                                                          (int)N, (int)K, accumulate);
+        } else {
+            dim3 grid((unsigned)((N + 31) / 32), (unsigned)((mp + 31) / 32));
+            gemm_f32_warpk_kernel<<<grid, 128, 0, stream>>>(Ap, lda, B, ldb, Cp, ldc, (int)mp, (int)N,
+                                                           (int)K, accumulate, vec_ok);
+        }
+        int rc = after_launch(ctx, "gemm_f32_kernel");
+        if (rc) return rc;
     }
-    return after_launch(ctx, "gemm_f32_kernel");
+    return GB200_OK;
 }
 
 }  // namespace gb200
@@ -233,7 +245,8 @@ extern "C" {
 int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
                    float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
                    void *stream) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, false);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -245,7 +258,8 @@ int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, 
 int gb200_gemm_f32_variant(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
                            float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
                            void *stream, int variant) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, false);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -255,7 +269,8 @@ int gb200_gemm_f32_variant(gb200_ctx *ctx, const float *A, int64_t lda, const fl
 
 int gb200_gemm_f32_host(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
                         float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, false);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -278,8 +293,7 @@ int gb200_gemm_f32_host(gb200_ctx *ctx, const float *A, int64_t lda, const float
     rc = gemm_f32_dispatch(ctx, dA, K, dB, N, dC, N, M, N, K, accumulate, s);
     if (rc) return rc;
     GB200_CUDA_TRY(cudaMemcpy2DAsync(C, ldc * 4, dC, N * 4, N * 4, M, cudaMemcpyDeviceToHost, s));
-    GB200_CUDA_TRY(cudaStreamSynchronize(s));
-    return GB200_OK;
+    return host_finish(ctx, s, nullptr);
 }
 
 }  // extern "C"

@@ -269,7 +269,8 @@ extern "C" {
 
 int gb200_softmax_rows_f32(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
                            int64_t ld_out, int64_t rows, int64_t cols, void *stream) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_softmax_args(in, ld_in, out, ld_out, rows, cols);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -281,7 +282,8 @@ int gb200_softmax_rows_f32(gb200_ctx *ctx, const float *in, int64_t ld_in, float
 int gb200_softmax_rows_f32_variant(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
                                    int64_t ld_out, int64_t rows, int64_t cols, void *stream,
                                    int variant) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_softmax_args(in, ld_in, out, ld_out, rows, cols);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -291,7 +293,8 @@ int gb200_softmax_rows_f32_variant(gb200_ctx *ctx, const float *in, int64_t ld_i
 
 int gb200_softmax_rows_f32_host(gb200_ctx *ctx, const float *in, int64_t ld_in, float *out,
                                 int64_t ld_out, int64_t rows, int64_t cols) {
-    int rc = enter(ctx);
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
     if (rc) return rc;
     rc = check_softmax_args(in, ld_in, out, ld_out, rows, cols);
     if (rc) return rc < 0 ? rc : GB200_OK;
@@ -319,9 +322,7 @@ int gb200_softmax_rows_f32_host(gb200_ctx *ctx, const float *in, int64_t ld_in, 
         GB200_CUDA_TRY(cudaMemcpy2DAsync(out + r0 * ld_out, ld_out * 4, d_out + r0 * dld, dld * 4,
                                          cols * 4, r1 - r0, cudaMemcpyDeviceToHost, down));
     }
-    GB200_CUDA_TRY(cudaStreamSynchronize(up));
-    GB200_CUDA_TRY(cudaStreamSynchronize(down));
-    return GB200_OK;
+    return host_finish(ctx, down, up);
 }
 
 }  // extern "C"

@@ -25,6 +25,10 @@
  *     Gern's single-stream hooks never overlap (src/codegen/codegen.cpp:576-611).
  *   - Status: 0 = success; negative = failure (see gb200_status).  A human-readable message
  *     for the calling thread's last failure is returned by gb200_last_error_string().
+ *   - The calling thread's current CUDA device is the same after a call as before it.
+ *   - A kernel whose bounded device-side wait ran out (a protocol error; the result is invalid) is
+ *     reported as GB200_ERR_TIMEOUT by the `_host` entry point itself, and for the device entry
+ *     points by the next gb200_device_sync().
  */
 #ifndef GERN_B200_H
 #define GERN_B200_H
@@ -122,10 +126,18 @@ int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const v
  * once, with the device current, before any stream capture begins.  All calls share the one
  * array: two calls whose kernels may overlap on the GPU (different streams) race on it; calls
  * on one stream are safe, and nothing a previous call left in the array is ever read.  Runs on
- * the calling thread's current device; does not synchronise. */
+ * the calling thread's current device, and A, B and C must be device memory of that device
+ * (anything else is refused with GB200_ERR_INVALID_ARG); does not synchronise.  A kernel whose
+ * bounded wait ran out leaves a wrong C and records the fact in a status word that
+ * gb200_static_status() reads. */
 int gb200_gemm_bf16_splitk_static(const void *A, int64_t lda, const void *B, int64_t ldb, void *C,
                                   int64_t ldc, int64_t M, int64_t N, int64_t K, int splits,
                                   void *stream);
+/* Status word of gb200_gemm_bf16_splitk_static on the current device: synchronises the device,
+ * returns GB200_OK when no kernel gave up a wait since the last query, else GB200_ERR_TIMEOUT with
+ * the kernel's code in *code (may be NULL), and clears the word.  Allocates nothing.  No
+ * counterpart in the reference. */
+int gb200_static_status(int *code);
 
 /* ---- row softmax ---------------------------------------------------------------------- */
 
@@ -160,7 +172,8 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
 /* O = softmax_rows(scale * Q K^T) V with bf16 Q (nq x d), K (nkv x d), V (nkv x d), O (nq x d),
  * all row-major; S and P stay in TMEM / shared memory.  d must be 128 in this build.  The
  * nearest reference analogue is the chained-GEMM fusion with a per-tile temporary
- * (test/test-cpu-mm.cpp:266-408). */
+ * (test/test-cpu-mm.cpp:266-408).  `scale` must be positive and finite (the row maximum is taken
+ * before scaling); anything else is refused with GB200_ERR_INVALID_ARG. */
 int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                          int64_t nkv, int64_t d, float scale, void *stream);
@@ -195,7 +208,10 @@ int gb200_attention_bf16_sharded(const gb200_shard *shards, int n, int64_t ldq, 
  * rows (>= 2) and shards[g].out receives as many output rows, except the last band, which
  * receives rows - 2.  Band g's kernel reads the first two rows of band g+1 directly from the
  * memory of the device that holds it (peer access is enabled on first use; ordinary loads over
- * NVLink, no copy, no extra launch). */
+ * NVLink, no copy, no extra launch).  Band g's kernel runs on shards[g].stream and reads band
+ * g+1's first two input rows without any ordering against the stream that produced them: every
+ * band's input must be complete (its producer synchronised, or an event of it waited on by
+ * shards[g].stream) before this call. */
 int gb200_blur3x3_f32_sharded(const gb200_shard *shards, int n, int64_t in_ld, int64_t in_cols,
                               int64_t out_ld);
 

@@ -23,8 +23,17 @@ _dp = ctypes.POINTER(ctypes.c_double)
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 
 
-def build(reference_dir: str | None = "/root/reference") -> None:
-    """Compiles the restatement and, when the reference tree is present, oracle/_ref."""
+def find_reference() -> str | None:
+    """The reference's source tree: $GERN_REFERENCE_DIR, else a directory named `reference` beside
+    this repository; None where neither holds the reference's src/."""
+    for cand in (os.environ.get("GERN_REFERENCE_DIR"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src")):
+            return cand
+    return None
+
+
+def build(reference_dir: str | None = None) -> None:
+    """Compiles the restatement and, when a reference tree is given, oracle/_ref."""
     subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
     if reference_dir and os.path.isdir(os.path.join(reference_dir, "src")):
         subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={reference_dir}"], check=True)

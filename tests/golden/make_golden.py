@@ -91,7 +91,7 @@ def reference_bf16_fixtures(ref):
 
 
 def main():
-    ref_dir = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("GERN_REFERENCE_DIR", "")
+    ref_dir = sys.argv[1] if len(sys.argv) > 1 else (pyoracle.find_reference() or "")
     if not os.path.isdir(os.path.join(ref_dir, "src")):
         raise SystemExit("usage: make_golden.py /path/to/reference  (or set GERN_REFERENCE_DIR)")
     pyoracle.build(ref_dir)

@@ -144,3 +144,17 @@ def test_host_entry_point(ctx, oracle):
     scale = 1.0 / np.sqrt(128.0)
     ctx.attention_bf16_host(q, k, v, o, scale)
     assert frob(pyoracle.bf16_bits_to_f32(o), oracle.attention_bf16(q, k, v, scale)) <= 1e-2
+
+
+@pytest.mark.parametrize("scale", [0.0, -0.1, float("nan"), float("inf")])
+def test_non_positive_or_non_finite_scale_is_refused(ctx, scale):
+    """The kernels scale the row maximum of the raw scores, which is only right for scale > 0."""
+    from gern_b200 import api
+    q, k, v = make(128, 128, 1)
+    o = torch.full((128, 128), 5.0, dtype=torch.bfloat16, device="cuda")
+    for variant in (None, 2):
+        with pytest.raises(api.GernB200Error) as e:
+            ctx.attention_bf16(q, k, v, o, scale, variant=variant)
+        assert e.value.code == -1 and "scale must be positive" in str(e.value)
+    ctx.sync()
+    assert bool((o == 5.0).all())

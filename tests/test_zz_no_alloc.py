@@ -3,7 +3,9 @@ the C ABI.  It serves callers that may not call cudaMalloc (see include/gern_b20
 workspace is a fixed array inside the library that every call shares.  The checks: two calls in a
 row with different shapes and split counts give exactly the bits of the context-based entry point
 (stale workspace contents must not leak into a later result), and an oversized request is refused
-with a clear error instead of overrunning the array.  Collected last on purpose."""
+with a clear error instead of overrunning the array; a warmed call leaves the device's free memory
+unchanged; operands that are not memory of the current device are refused.  Collected last on
+purpose."""
 import numpy as np
 import pytest
 import torch
@@ -64,3 +66,71 @@ def test_requests_beyond_the_fixed_workspace_are_refused():
     torch.cuda.synchronize()
     ref = a.float() @ b.float().T
     assert float(torch.linalg.norm(c.float() - ref) / torch.linalg.norm(ref)) <= 3e-3
+
+
+@pytest.mark.parametrize("mnk,splits", [((200, 330, 2048), 3),     # N % 4 != 0: scalar slab stores and reduce
+                                        ((128, 256, 128), 4),      # more splits than 64-wide K blocks: empty slabs
+                                        ((512, 512, 8192), 0)])    # library-chosen split count
+def test_slab_paths_match_the_context_entry_point(ctx, mnk, splits):
+    from gern_b200 import api
+    m, n, k = mnk
+    # a call that leaves the shared array full of another problem's partial sums comes first
+    af, bf = make(512, 512, 4096, seed=9)
+    api.gemm_bf16_splitk_static(af, bf, torch.empty((512, 512), dtype=torch.bfloat16, device="cuda"), splits=8)
+    a, b = make(m, n, k, seed=m + n + k)
+    want = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    got = torch.zeros_like(want)
+    ctx.gemm_bf16(a, b, want, splits=splits)
+    api.gemm_bf16_splitk_static(a, b, got, splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    api.static_status()      # no kernel gave up a wait
+
+
+def test_a_warmed_call_allocates_no_device_memory(ctx):
+    from gern_b200 import api
+    a, b = make(512, 512, 4096, seed=4)
+    c = torch.zeros((512, 512), dtype=torch.bfloat16, device="cuda")
+    api.gemm_bf16_splitk_static(a, b, c, splits=8)           # first call on the device: set-up
+    api.static_status()
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    for splits in (8, 2, 0, 1):
+        api.gemm_bf16_splitk_static(a, b, c, splits=splits)
+    api.static_status()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0, "the entry point changed the device's free memory"
+
+
+def test_operands_outside_the_current_device_are_refused():
+    from gern_b200 import api
+    a, b = make(128, 256, 256, seed=5)
+    c = torch.full((128, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    host_a = torch.zeros((128, 256), dtype=torch.bfloat16).pin_memory()
+    with pytest.raises(api.GernB200Error) as e:
+        api.gemm_bf16_splitk_static(host_a, b, c, splits=1)
+    assert e.value.code == -1 and "not device memory of the current device" in str(e.value)
+    torch.cuda.synchronize()
+    assert bool((c == 7.0).all())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_second_device_has_its_own_array(ctx):
+    from gern_b200 import api
+    with torch.cuda.device(1):
+        g = torch.Generator(device="cuda:1").manual_seed(6)
+        a = (torch.randn((256, 2048), generator=g, device="cuda:1") * 0.02).to(torch.bfloat16)
+        b = (torch.randn((512, 2048), generator=g, device="cuda:1") * 0.02).to(torch.bfloat16)
+        c = torch.zeros((256, 512), dtype=torch.bfloat16, device="cuda:1")
+        api.gemm_bf16_splitk_static(a, b, c, splits=4)
+        api.static_status()
+        torch.cuda.synchronize()
+        ref = a.float() @ b.float().T
+        assert float(torch.linalg.norm(c.float() - ref) / torch.linalg.norm(ref)) <= 3e-3
+        # a context call on device 0 in between must not move this thread off device 1
+        x = torch.zeros((64, 64), device="cuda:0")
+        ctx.softmax_rows(x, torch.empty_like(x))
+        assert torch.cuda.current_device() == 1
+        c0 = torch.zeros((128, 256), dtype=torch.bfloat16, device="cuda:0")
+        with pytest.raises(api.GernB200Error):
+            api.gemm_bf16_splitk_static(a[:128, :256].contiguous(), b[:256, :256].contiguous(), c0, splits=1)
