@@ -1,0 +1,143 @@
+"""libgern_b200 behind the UNMODIFIED Gern front end: integration/gern/b200.h (annotations) and
+gb200_host.h (run-time objects) are composed into Gern programs by integration/gern/run_program.cpp,
+lowered by the reference's own Runner::compile (code generation, g++, dlopen) and run by
+Runner::evaluate -- the flow of the reference's test/test-cpu-mm.cpp:13-83 with the library behind
+the leaf function.
+
+The driver links the reference's library objects, so it is built only where the Gern tree is present
+(`make -C integration/gern`, also done by __graft_entry__.build()); the built binary travels with the
+tree.  Without it these tests are skipped with that reason.  CPU part: every program is generated,
+compiled, linked and loaded, and evaluate reaches the library, which reports that there is no
+device.  GPU part: results against the oracle and the reference-made fixtures."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+RUNNER = os.path.join(ROOT, "integration", "_ref", "gern_b200_runner")
+
+needs_runner = pytest.mark.skipif(not os.path.exists(RUNNER),
+                                  reason="integration/_ref/gern_b200_runner not built (needs the Gern tree at build time)")
+
+
+def run(space, program, *args, cwd):
+    cmd = [RUNNER, "--repo", ROOT, space, program] + [str(a) for a in args]
+    return subprocess.run(cmd, capture_output=True, text=True, cwd=cwd, timeout=600)
+
+
+def have_gpu():
+    import torch
+    return torch.cuda.is_available()
+
+
+PROGRAMS = {
+    "blur": (lambda d: [40, 52, 8, d / "in.bin", d / "out.bin"], "gb200_host::blur3x3(", {"in.bin": (40 * 52, np.float32)}),
+    "mm": (lambda d: [64, 64, 64, 32, 32, 32, d / "a.bin", d / "b.bin", d / "c.bin"], "gb200_host::matrix_multiply(",
+           {"a.bin": (64 * 64, np.float32), "b.bin": (64 * 64, np.float32)}),
+    "mm_bf16": (lambda d: [64, 64, 64, 32, 32, d / "a.bin", d / "b.bin", d / "c.bin"], "gb200_host::matrix_multiply_bf16(",
+                {"a.bin": (64 * 64, np.uint16), "b.bin": (64 * 64, np.uint16)}),
+    "softmax": (lambda d: [64, 64, 16, d / "in.bin", d / "out.bin"], "gb200_host::softmax_rows(", {"in.bin": (64 * 64, np.float32)}),
+    "attention": (lambda d: [128, 256, 64, 0.125, d / "q.bin", d / "k.bin", d / "v.bin", d / "o.bin"], "gb200_host::attention(",
+                  {"q.bin": (128 * 128, np.uint16), "k.bin": (256 * 128, np.uint16), "v.bin": (256 * 128, np.uint16)}),
+}
+
+
+@needs_runner
+@pytest.mark.parametrize("program", sorted(PROGRAMS))
+def test_runner_generates_compiles_and_loads_every_program(tmp_path, program):
+    """No GPU needed: Runner::compile must succeed (the hook is generated, compiled against
+    gb200_host.h, linked with -lgern_b200 and dlopen'ed) and evaluate must reach the library."""
+    make_args, call, files = PROGRAMS[program]
+    for name, (count, dtype) in files.items():
+        np.zeros(count, dtype).tofile(tmp_path / name)
+    res = run("host", program, *make_args(tmp_path), cwd=tmp_path)
+    assert "compiled: /tmp/gern_b200_" + program + "_host.cpp" in res.stdout, res.stderr
+    src = open(f"/tmp/gern_b200_{program}_host.cpp").read()
+    assert call in src and 'extern "C"' in src and "hook_function_" in src
+    assert '#include "gb200_host.h"' in src and '#include "gern_b200.h"' in src
+    if have_gpu():
+        assert res.returncode == 0, res.stderr
+    else:
+        # the library is reached and refuses loudly: GB200_ERR_NO_DEVICE, never a CPU fallback
+        assert res.returncode == 4
+        assert "status -4" in res.stderr and "no CUDA device" in res.stderr
+
+
+@needs_runner
+def test_softmax_annotation_puts_its_whole_row_assumption_into_the_emitted_code(tmp_path):
+    """The RowSoftmax annotation assumes l_y == output.col; Gern prints the assumption as an assert
+    at the top of the generated function."""
+    np.zeros(64 * 64, np.float32).tofile(tmp_path / "in.bin")
+    run("host", "softmax", 64, 64, 16, tmp_path / "in.bin", tmp_path / "out.bin", cwd=tmp_path)
+    src = open("/tmp/gern_b200_softmax_host.cpp").read()
+    assert "assert((output.col == output.col))" in src.replace("  ", " ")
+
+
+# ---------------------------------------------------------------------------------------------
+gpu = pytest.mark.gpu
+
+
+@needs_runner
+@gpu
+@pytest.mark.parametrize("space", ["host", "device"])
+@pytest.mark.parametrize("rows,cols,band", [(514, 1030, 0), (514, 1030, 128), (66, 70, 16)])
+def test_blur_through_gern_matches_the_oracle(tmp_path, oracle, space, rows, cols, band):
+    x = np.random.default_rng(rows + cols).random((rows, cols), dtype=np.float32)
+    x.tofile(tmp_path / "in.bin")
+    res = run(space, "blur", rows, cols, band, tmp_path / "in.bin", tmp_path / "out.bin", cwd=tmp_path)
+    assert res.returncode == 0, res.stderr
+    got = np.fromfile(tmp_path / "out.bin", np.float32).reshape(rows - 2, cols - 2)
+    assert np.array_equal(got, oracle.blur_xy(x))
+
+
+@needs_runner
+@gpu
+@pytest.mark.parametrize("space", ["host", "device"])
+def test_fp32_matmul_512_through_gern_matches_gerns_cpu_path(tmp_path, golden, space):
+    """Configuration 0 (512^3, A = B = random_fill(-1, 1)), tiled 256 / 256 / 256 under Gern's
+    Tile / Reduce, against the fixture Gern's own CPU path produced (tiles 64 / 64 / 64): the
+    apps' bar |delta| < 1e-3 (gernels/mm/float-error.h) and relative Frobenius error < 1e-5."""
+    from oracle import pyoracle
+    a = pyoracle.mt19937_uniform(512 * 512, -1.0, 1.0).reshape(512, 512)
+    a.tofile(tmp_path / "a.bin")
+    res = run(space, "mm", 512, 512, 512, 256, 256, 256, tmp_path / "a.bin", tmp_path / "a.bin", tmp_path / "c.bin", cwd=tmp_path)
+    assert res.returncode == 0, res.stderr
+    c = np.fromfile(tmp_path / "c.bin", np.float32).reshape(512, 512)
+    want = golden["mm512_sub"]
+    got = c[::8, ::8]
+    assert np.abs(got - want).max() < 1e-3
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-5
+    assert abs(c.astype(np.float64).sum() - float(golden["mm512_sum"])) < 1e-3 * 512
+
+
+@needs_runner
+@gpu
+def test_bf16_matmul_softmax_and_chain_through_gern(tmp_path, oracle, golden, golden_maker):
+    from oracle import pyoracle
+    a, b = golden_maker.bf16_inputs("gemm512")
+    a.tofile(tmp_path / "a.bin")
+    b.tofile(tmp_path / "b.bin")
+    res = run("device", "mm_bf16", 512, 512, 512, 256, 256, tmp_path / "a.bin", tmp_path / "b.bin", tmp_path / "c.bin", cwd=tmp_path)
+    assert res.returncode == 0, res.stderr
+    c = pyoracle.bf16_bits_to_f32(np.fromfile(tmp_path / "c.bin", np.uint16).reshape(512, 512))
+    want = golden["gemmbf512_sub"]
+    assert np.linalg.norm(c[::8, ::8] - want) / np.linalg.norm(want) <= 3e-3
+
+    x = (np.random.default_rng(5).standard_normal((256, 4096)) * 3).astype(np.float32)
+    x.tofile(tmp_path / "in.bin")
+    res = run("device", "softmax", 256, 4096, 64, tmp_path / "in.bin", tmp_path / "out.bin", cwd=tmp_path)
+    assert res.returncode == 0, res.stderr
+    got = np.fromfile(tmp_path / "out.bin", np.float32).reshape(256, 4096)
+    ref = oracle.softmax_rows(x)
+    assert (np.abs(got.astype(np.float64) - ref) / np.maximum(ref, 1e-30)).max() <= 1e-5
+
+    q, k, v = golden_maker.bf16_inputs("attn")
+    for name, t in (("q.bin", q), ("k.bin", k), ("v.bin", v)):
+        t.tofile(tmp_path / name)
+    res = run("host", "attention", 64, 256, 32, golden_maker.ATTN_SCALE, tmp_path / "q.bin", tmp_path / "k.bin",
+              tmp_path / "v.bin", tmp_path / "o.bin", cwd=tmp_path)
+    assert res.returncode == 0, res.stderr
+    o = pyoracle.bf16_bits_to_f32(np.fromfile(tmp_path / "o.bin", np.uint16).reshape(64, 128))
+    assert np.linalg.norm(o - golden["attn_o"]) / np.linalg.norm(golden["attn_o"]) <= 1e-2
