@@ -374,11 +374,15 @@ class SoftmaxWorkload(Workload):
         torch = self.torch
         idx = spread_rows(self.rows, 64)
         sel = torch.tensor(idx, device="cuda")
-        want = oracle.softmax_rows(np.ascontiguousarray(self.x[sel].cpu().numpy()))
-        got = self.out[sel].cpu().numpy()
-        rel = float((np.abs(got.astype(np.float64) - want) / np.maximum(np.abs(want), 1e-30)).max())
-        ok = rel <= 1e-5
-        return len(idx), ok, "" if ok else f"rank {self.rank}: softmax rel err {rel:.3g} > 1e-5"
+        xs = np.ascontiguousarray(self.x[sel].cpu().numpy())
+        got = self.out[sel].cpu().numpy().astype(np.float64)
+        rel_of = lambda want: float((np.abs(got - want) / np.maximum(np.abs(want), 1e-30)).max())
+        # 1e-5 against the exact softmax; against the fp32 oracle, 1e-5 plus the drift of its
+        # sequential fp32 row sum (the reference's sum_row) from the exact value on the same rows
+        exact, want = oracle.softmax_rows_f64(xs), oracle.softmax_rows(xs)
+        drift = float((np.abs(want - exact) / np.maximum(exact, 1e-30)).max())
+        ok = rel_of(exact) <= 1e-5 and rel_of(want) <= 1e-5 + drift
+        return len(idx), ok, "" if ok else f"rank {self.rank}: softmax rel err {rel_of(want):.3g} vs oracle, {rel_of(exact):.3g} vs fp64"
 
     def e2e_setup(self):
         torch = self.torch
@@ -1063,6 +1067,10 @@ def main():
                                  "one_gpu_ms_per_step", "speedup_vs_one_gpu", "scaling") if k in r}
         return out
 
+    # The side workloads follow one another with host work (allocation, the oracle) in between, and
+    # a sub-100-us kernel measured 5 % slower on its first launches after such a pause than once the
+    # GPU had been busy for a few milliseconds: they warm up longer than the headline's W.
+    SIDE_WARMUP = 50
     main_mode = "single" if world == 1 else "weak"
     main_res = run_workload(args.workload, main_mode, args.steps, args.warmup, not args.no_e2e, not args.no_cpu_baseline)
     also = {}
@@ -1070,17 +1078,17 @@ def main():
     for name in [s for s in args.also.split(",") if s in WORKLOADS and s != args.workload]:
         try:
             if world == 1:
-                also[name] = brief(run_workload(name, "single", side_steps, 5, not args.no_e2e, not args.no_cpu_baseline))
+                also[name] = brief(run_workload(name, "single", side_steps, SIDE_WARMUP, not args.no_e2e, not args.no_cpu_baseline))
             elif WORKLOADS[name].sharded:
-                weak = brief(run_workload(name, "weak", side_steps, 5, False, False))
+                weak = brief(run_workload(name, "weak", side_steps, SIDE_WARMUP, False, False))
                 weak["scaling"] = "weak"
-                also[name] = {"weak": weak, "strong": brief(strong_with_reference(name, side_steps, 5))}
+                also[name] = {"weak": weak, "strong": brief(strong_with_reference(name, side_steps, SIDE_WARMUP))}
         except Exception as e:  # a failing side workload must not hide the headline line
             also[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
             failures.append(f"{name}: {e}")
     if world > 1 and WORKLOADS[args.workload].sharded and args.also:
         try:
-            also[args.workload + "_strong"] = brief(strong_with_reference(args.workload, side_steps, 5))
+            also[args.workload + "_strong"] = brief(strong_with_reference(args.workload, side_steps, SIDE_WARMUP))
         except Exception as e:  # noqa: BLE001
             also[args.workload + "_strong"] = {"error": f"{type(e).__name__}: {e}"[:300]}
             failures.append(f"{args.workload}_strong: {e}")

@@ -32,6 +32,7 @@ SIGNATURES = {
     "gb200_gemm_f32": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
     "gb200_gemm_f32_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp, _int],
     "gb200_gemm_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp],
+    "gb200_gemm_bf16_cluster": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp],
     "gb200_gemm_bf16_splitk": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
     "gb200_gemm_bf16_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _vp, _int],
     "gb200_gemm_bf16_splitk_static": None,
@@ -64,6 +65,23 @@ lib.gb200_gemm_bf16_splitk_static.restype = _int
 lib.gb200_static_status.argtypes = [ctypes.POINTER(_int)]
 lib.gb200_static_status.restype = _int
 SIGNATURES["gb200_static_status"] = None
+
+
+class KernelResources(ctypes.Structure):
+    """gb200_kernel_resources."""
+    _fields_ = [("regs_per_thread", _int), ("threads", _int), ("dynamic_smem_bytes", _int), ("cluster_x", _int),
+                ("tmem_columns", _int)]
+
+
+lib.gb200_kernel_resources_query.argtypes = [ctypes.c_char_p, ctypes.POINTER(KernelResources)]
+lib.gb200_kernel_resources_query.restype = _int
+SIGNATURES["gb200_kernel_resources_query"] = None
+
+
+def kernel_resources(name: str) -> KernelResources:
+    out = KernelResources()
+    _check(lib.gb200_kernel_resources_query(name.encode(), ctypes.byref(out)), "gb200_kernel_resources_query")
+    return out
 
 
 class GemmEpilogue(ctypes.Structure):

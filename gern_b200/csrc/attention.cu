@@ -25,6 +25,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "smem_plan.hpp"
 
 namespace gb200 {
 
@@ -35,8 +36,13 @@ constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: any 128 x 128 bf16 tile (2
 constexpr int CHUNK_BYTES = 128 * 128;     // 16 KiB: 128 rows x 64 bf16
 constexpr int KV_SLOTS = 5;                // one ring for K_0 V_0 K_1 V_1 ...
 constexpr int NUM_THREADS = 320;           // 8 softmax warps + MMA warp + TMA warp
-// Q (2 tiles), K/V ring, then barriers
-constexpr int SMEM_BYTES = (TILES + KV_SLOTS) * TILE_BYTES + 1024 + 256;
+// Q (2 tiles), K/V ring, then barriers and the TMEM slot
+constexpr smem::AttentionLayout kLayout = smem::attention_layout(NUM_THREADS, 0);
+static_assert(smem::AttentionLayout::kTiles == TILES && smem::AttentionLayout::kKvSlots == KV_SLOTS &&
+                  smem::AttentionLayout::kTileBytes == TILE_BYTES && kLayout.q.offset == 0 &&
+                  kLayout.kv.offset == TILES * TILE_BYTES,
+              "kernel and planner disagree");
+constexpr int SMEM_BYTES = kLayout.dynamic_bytes;
 // S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t (bf16 pairs) overwrites S_t's first 64
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -127,15 +133,15 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char *sQ = smem;                               // [TILES] tiles
     unsigned char *sKV = smem + TILES * TILE_BYTES;         // [KV_SLOTS] tiles
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (TILES + KV_SLOTS) * TILE_BYTES);
-    uint64_t *q_full = bars;                      // [1]
-    uint64_t *kv_full = bars + 1;                 // [KV_SLOTS]
-    uint64_t *kv_empty = kv_full + KV_SLOTS;      // [KV_SLOTS]
-    uint64_t *s_full = kv_empty + KV_SLOTS;       // [2] MMA -> softmax t: S_t holds block j
-    uint64_t *sp_ready = s_full + TILES;          // [2] softmax t -> MMA: P_t written over S_t
-    uint64_t *o_full = sp_ready + TILES;          // [2] MMA -> softmax t: O_t final
-    uint64_t *p_half = o_full + TILES;            // [2] softmax t -> MMA: kv 0-63 of P_t written
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(p_half + TILES);
+    auto bar_at = [&](int offset) { return reinterpret_cast<uint64_t *>(smem + offset); };
+    uint64_t *q_full = bar_at(kLayout.q_full.offset);        // [1]
+    uint64_t *kv_full = bar_at(kLayout.kv_full.offset);      // [KV_SLOTS]
+    uint64_t *kv_empty = bar_at(kLayout.kv_empty.offset);    // [KV_SLOTS]
+    uint64_t *s_full = bar_at(kLayout.s_full.offset);        // [2] MMA -> softmax t: S_t holds block j
+    uint64_t *sp_ready = bar_at(kLayout.sp_ready.offset);    // [2] softmax t -> MMA: P_t written over S_t
+    uint64_t *o_full = bar_at(kLayout.o_full.offset);        // [2] MMA -> softmax t: O_t final
+    uint64_t *p_half = bar_at(kLayout.p_half.offset);        // [2] softmax t -> MMA: kv 0-63 of P_t written
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kLayout.tmem_slot.offset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * (BM * TILES);
@@ -455,11 +461,15 @@ int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void
                           const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
                           int64_t d, float scale, cudaStream_t stream);
 
+int attention_split_launch(gb200_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
+                           void *O, int64_t ldo, int64_t nq, int64_t nkv, float scale, cudaStream_t stream);
+
 #ifndef GB200_ATTN_AUTO_PAIR
 #define GB200_ATTN_AUTO_PAIR 0
 #endif
 
-// kernel_choice: 0 = pick, 1 = one CTA per two Q tiles, 2 = CTA pairs (attention_pair.cu).
+// kernel_choice: 0 = pick, 1 = one CTA per two Q tiles and one softmax thread per row, 2 = CTA pairs
+// (attention_pair.cu), 3 = one CTA per two Q tiles and two softmax threads per row (attention_split.cu).
 int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                        const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
                        int64_t d, float scale, cudaStream_t stream, int kernel_choice = 0) {
@@ -479,6 +489,8 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     rc = get_tmap_2d(ctx, V, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)d, (uint64_t)nkv,
                      (uint64_t)ldv * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tv);
     if (rc) return rc;
+    if (kernel_choice == 3)
+        return attention_split_launch(ctx, tq, tk, tv, O, ldo, nq, nkv, scale, stream);
     rc = ensure_dynamic_smem(ctx, attention_bf16_kernel, SMEM_BYTES);
     if (rc) return rc;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -505,6 +517,8 @@ static int check_attention_args(const void *Q, int64_t ldq, const void *K, int64
                   "leading dimension smaller than the row");
     return GB200_OK;
 }
+
+int kernel_regs_attention() { return kernel_registers(attention_bf16_kernel); }
 
 }  // namespace gb200
 

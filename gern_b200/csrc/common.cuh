@@ -126,6 +126,16 @@ inline int ensure_dynamic_smem(gb200_ctx *ctx, Kernel kernel, int bytes) {
     ctx->smem_attr_done.insert(key);
     return GB200_OK;
 }
+// Registers per thread of `kernel` as compiled, or -1 where the CUDA runtime cannot tell (no device).
+template <typename Kernel>
+inline int kernel_registers(Kernel kernel) {
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return attr.numRegs;
+}
 // Grows staging slot `slot` to at least `bytes`.
 int stage_reserve(gb200_ctx *ctx, int slot, size_t bytes);
 // Grows the context's kernel workspace to at least `bytes`.

@@ -22,16 +22,21 @@
 // Every wait is bounded; a wait that runs out records a code in the context's status word and
 // the kernel winds down (TMEM is always freed).
 #include "common.cuh"
+#include "smem_plan.hpp"
 
 namespace gb200 {
 
 namespace gemm {
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+using Layout = smem::GemmTcLayout;
+constexpr int BM = Layout::kBM, BN = 256, BK = Layout::kBK, STAGES = Layout::kStages;
 constexpr int A_BYTES = BM * BK * 2;              // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;              // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;    // 48 KiB
-constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = Layout::kThreads;
+// stage ring, barriers, TMEM slot: one planned layout per tile width
+template <int TILE_N>
+constexpr smem::GemmTcLayout kLayout = smem::gemm_tc_layout(TILE_N);
+constexpr int SMEM_BYTES = kLayout<BN>.dynamic_bytes;
 #ifndef GB200_GEMM_AUTO_PAIR
 #define GB200_GEMM_AUTO_PAIR 1
 #endif
@@ -106,12 +111,12 @@ gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
-    uint64_t *full = bars;                  // [STAGES] TMA -> MMA
-    uint64_t *empty = bars + STAGES;        // [STAGES] MMA -> TMA
-    uint64_t *acc_full = bars + 2 * STAGES;       // [2] MMA -> epilogue
-    uint64_t *acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
-    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    static_assert(kLayout<BN>.stage_bytes == STAGE_BYTES && kLayout<BN>.stages.offset == 0, "kernel and planner disagree");
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kLayout<BN>.full.offset);            // [STAGES] TMA -> MMA
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + kLayout<BN>.empty.offset);          // [STAGES] MMA -> TMA
+    uint64_t *acc_full = reinterpret_cast<uint64_t *>(smem + kLayout<BN>.acc_full.offset);    // [2] MMA -> epilogue
+    uint64_t *acc_empty = reinterpret_cast<uint64_t *>(smem + kLayout<BN>.acc_empty.offset);  // [2] epilogue -> MMA
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(smem + kLayout<BN>.tmem_slot.offset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
@@ -442,7 +447,7 @@ template <int TILE_N>
 static int launch_tc_plain(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                            void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
     using namespace gemm;
-    constexpr int smem_bytes = STAGES * (A_BYTES + TILE_N * BK * 2) + 1024 + 256;
+    constexpr int smem_bytes = gemm::kLayout<TILE_N>.dynamic_bytes;
     CUtensorMap ta, tb;
     int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                          (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
@@ -464,7 +469,7 @@ template <int TILE_N>
 static int launch_tc_f32x3(gb200_ctx *ctx, const void *A3, const void *B3, float *C, int64_t ldc,
                            int64_t M, int64_t N, int64_t Kp, int accumulate, cudaStream_t stream) {
     using namespace gemm;
-    constexpr int smem_bytes = STAGES * (A_BYTES + TILE_N * BK * 2) + 1024 + 256;
+    constexpr int smem_bytes = gemm::kLayout<TILE_N>.dynamic_bytes;
     CUtensorMap ta, tb;
     int rc = get_tmap_2d(ctx, A3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)(3 * Kp), (uint64_t)M,
                          (uint64_t)(3 * Kp) * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
@@ -608,6 +613,8 @@ int gemm_bf16_epilogue_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, cons
     return after_launch(ctx, "gemm_bf16_tc_kernel<epilogue>");
 }
 
+int kernel_regs_gemm_tc() { return kernel_registers(gemm_bf16_tc_kernel<false>); }
+
 }  // namespace gb200
 
 using namespace gb200;
@@ -651,6 +658,20 @@ int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, i
     if (rc) return rc < 0 ? rc : GB200_OK;
     return gemm_bf16_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K,
                               static_cast<cudaStream_t>(stream));
+}
+
+int gb200_gemm_bf16_cluster(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                            void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int cluster_x,
+                            void *stream) {
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(cluster_x == 1 || cluster_x == 2, GB200_ERR_UNSUPPORTED,
+                  "the bf16 GEMM has kernels for clusters of 1 and 2 thread blocks (asked for %d)", cluster_x);
+    rc = check_gemm_args(A, lda, B, ldb, C, ldc, M, N, K, true);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return gemm_bf16_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, static_cast<cudaStream_t>(stream), 1,
+                              cluster_x);
 }
 
 // Test / benchmark hook: same contract with the number of K splits chosen by the caller

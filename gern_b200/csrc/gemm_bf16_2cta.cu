@@ -13,6 +13,7 @@
 // cluster barriers at start and end are the only unbounded synchronisation and are reached by
 // every thread on every path.
 #include "common.cuh"
+#include "smem_plan.hpp"
 
 namespace gb200 {
 
@@ -29,8 +30,10 @@ constexpr int HALF = 128;                            // rows of A / of B per CTA
 constexpr int A_BYTES = HALF * BK * 2;               // 16 KiB
 constexpr int B_BYTES = HALF * BK * 2;               // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 32 KiB per CTA
-constexpr int NUM_THREADS = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int NUM_THREADS = smem::Gemm2CtaLayout::kThreads;
+constexpr smem::Gemm2CtaLayout kLayout = smem::gemm_2cta_layout(STAGES);
+static_assert(kLayout.stage_bytes == STAGE_BYTES && kLayout.stages.offset == 0, "kernel and planner disagree");
+constexpr int SMEM_BYTES = kLayout.dynamic_bytes;
 constexpr int GROUP_M = GB200_GEMM2_GROUP_M;         // 256-row tile rows per rasterisation group
 }  // namespace gemm2
 
@@ -62,12 +65,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * STAGE_BYTES);
-    uint64_t *full = bars;                        // [STAGES] used in the leader only
-    uint64_t *empty = bars + STAGES;              // [STAGES] one per CTA
-    uint64_t *acc_full = bars + 2 * STAGES;       // [2] one per CTA
-    uint64_t *acc_empty = bars + 2 * STAGES + 2;  // [2] used in the leader only (8 arrivals)
-    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + kLayout.full.offset);            // [STAGES] used in the leader only
+    uint64_t *empty = reinterpret_cast<uint64_t *>(smem + kLayout.empty.offset);          // [STAGES] one per CTA
+    uint64_t *acc_full = reinterpret_cast<uint64_t *>(smem + kLayout.acc_full.offset);    // [2] one per CTA
+    uint64_t *acc_empty = reinterpret_cast<uint64_t *>(smem + kLayout.acc_empty.offset);  // [2] used in the leader only (8 arrivals)
+    uint32_t *tmem_base_slot = reinterpret_cast<uint32_t *>(smem + kLayout.tmem_slot.offset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -304,5 +306,7 @@ int gemm_f32x3_2cta_launch(gb200_ctx *ctx, const void *A3, const void *B3, float
                               (int64_t)0, (int)M, (int)N, (int)(6 * Kp), ctx->d_status, f32));
     return after_launch(ctx, "gemm_bf16_2cta_kernel<f32x3>");
 }
+
+int kernel_regs_gemm_2cta() { return kernel_registers(gemm_bf16_2cta_kernel<false>); }
 
 }  // namespace gb200

@@ -52,18 +52,31 @@ public:
             throw error::UserError("libgern_b200 holds sm_100a code only (arch=" + config.arch + ")");
         calls.clear();
         launch_args.clear();
+        smem_request = -1;
         std::set<int> units;
         bool in_global = false;
         flatten(c, units, in_global);
         if (calls.empty()) throw error::UserError("empty program");
         lower();
+        bindLaunch();
         compiled = true;
     }
+
+    // What the planned kernel allocates per thread block (registers, threads, dynamic shared memory,
+    // cluster size, TMEM columns): the library's answer to Gern's Allocates(reg, smem)
+    // (include/gern/annotations/stmt.h:113-121).  Defined for the TMA / tcgen05 kernels.
+    bool hasResources() const { return !kernel_name.empty(); }
+    const gb200_kernel_resources &resources() const { return kernel_resources; }
+    const std::string &kernelName() const { return kernel_name; }
+    // Thread blocks per cluster the program pinned with Global({{CLUSTER_DIM_X, v}}), 0 = not pinned.
+    int clusterX() const { return cluster_x; }
 
     Kernel kernel() const { return plan; }
     std::vector<std::string> argumentOrder() const { return argument_order; }
 
-    // Launch dimensions pinned by Global(), by dimension (checked, recorded, advisory).
+    // Launch dimensions pinned by Global(), by dimension.  CLUSTER_DIM_X selects the kernel (see
+    // bindLaunch); grid and block dimensions are checked and recorded: the library's kernels size
+    // their own persistent grids.
     const std::map<Grid::Dim, int64_t> &launchArgs() const { return launch_args; }
 
     void evaluate(std::map<std::string, void *> args) { evaluate(std::move(args), nullptr); }
@@ -92,7 +105,11 @@ public:
                 auto &A = M(names[0]), &B = M(names[1]), &C = M(names[2]);
                 // B is a column-major K x N matrix: its object holds N rows of K values.
                 require(A.col == B.col && C.row == A.row && C.col == B.row, "matrix_multiply: shapes do not agree");
-                rc = gb200_gemm_bf16(ctx, A.data, A.lda, B.data, B.lda, C.data, C.lda, C.row, C.col, A.col, stream);
+                if (cluster_x > 0)
+                    rc = gb200_gemm_bf16_cluster(ctx, A.data, A.lda, B.data, B.lda, C.data, C.lda, C.row, C.col,
+                                                 A.col, cluster_x, stream);
+                else
+                    rc = gb200_gemm_bf16(ctx, A.data, A.lda, B.data, B.lda, C.data, C.lda, C.row, C.col, A.col, stream);
                 break;
             }
             case Kernel::Blur: {
@@ -174,8 +191,11 @@ private:
                     if (kv.second.getInt64Val() <= 0) throw error::UserError("Global: launch dimensions are positive");
                     launch_args[kv.first] = kv.second.getInt64Val();
                 }
-                if (p->smem_size.defined() && p->smem_size.isBound() && p->smem_size.getInt64Val() > 227 * 1024)
-                    throw error::UserError("Global: more dynamic shared memory than an sm_100a block can have (227 KB)");
+                if (p->smem_size.defined() && p->smem_size.isBound()) {
+                    if (p->smem_size.getInt64Val() > 227 * 1024)
+                        throw error::UserError("Global: more dynamic shared memory than an sm_100a block can have (227 KB)");
+                    smem_request = p->smem_size.getInt64Val();
+                }
                 flatten(p->children[0], units, true);
                 return;
             case Node::Stage: flatten(p->children[0], units, in_global); return;
@@ -209,6 +229,44 @@ private:
                 return;
             }
         }
+    }
+
+    // Turns what Global() pinned into the launch: the cluster dimension picks between the kernels
+    // the library has for the planned operator, and the program's shared-memory request is held
+    // against the planned layout of that kernel.
+    void bindLaunch() {
+        cluster_x = 0;
+        kernel_name.clear();
+        for (Grid::Dim d : {Grid::CLUSTER_DIM_Y, Grid::CLUSTER_DIM_Z}) {
+            auto it = launch_args.find(d);
+            if (it != launch_args.end() && it->second != 1)
+                throw error::UserError("Global: the library's kernels form clusters along x only");
+        }
+        auto cx = launch_args.find(Grid::CLUSTER_DIM_X);
+        if (cx != launch_args.end()) cluster_x = static_cast<int>(cx->second);
+        switch (plan) {
+            case Kernel::GemmBF16:
+                if (cluster_x != 0 && cluster_x != 1 && cluster_x != 2)
+                    throw error::UserError("Global: the bf16 matrix_multiply has kernels for clusters of 1 and 2 "
+                                           "thread blocks, not " + std::to_string(cluster_x));
+                // not pinned: the library picks by problem size; report the pair kernel's needs (the larger)
+                kernel_name = cluster_x == 1 ? "gemm_bf16_tc" : "gemm_bf16_2cta";
+                break;
+            case Kernel::GemmEpilogue: kernel_name = "gemm_bf16_tc"; break;
+            case Kernel::Attention: kernel_name = "attention_bf16"; break;
+            default: break;
+        }
+        if (plan != Kernel::GemmBF16 && cluster_x > 1)
+            throw error::UserError("Global: only the bf16 matrix_multiply has a kernel for clusters of " +
+                                   std::to_string(cluster_x) + " thread blocks");
+        if (kernel_name.empty()) return;
+        if (gb200_kernel_resources_query(kernel_name.c_str(), &kernel_resources) != 0)
+            throw error::InternalError(std::string("libgern_b200: ") + gb200_last_error_string());
+        if (smem_request >= 0 && smem_request < kernel_resources.dynamic_smem_bytes)
+            throw error::UserError("Global: kernel " + kernel_name + " needs " +
+                                   std::to_string(kernel_resources.dynamic_smem_bytes) +
+                                   " bytes of dynamic shared memory, the program asks for " +
+                                   std::to_string(smem_request));
     }
 
     bool isChain(size_t at, AbstractDataTypePtr &in, AbstractDataTypePtr &out) const {
@@ -335,6 +393,10 @@ private:
     }
 
     std::map<Grid::Dim, int64_t> launch_args;
+    int64_t smem_request = -1;   // Global(..., smem_size), -1 = none
+    int cluster_x = 0;
+    std::string kernel_name;
+    gb200_kernel_resources kernel_resources{};
     std::string epi_sub, epi_div, epi_max, epi_sum, epi_c;
     bool epi_exp = false;
     Composable c;

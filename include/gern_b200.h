@@ -68,6 +68,22 @@ const char *gb200_version(void);
 /* Number of kernels this library has launched on behalf of `ctx` since it was created. */
 int64_t gb200_launch_count(gb200_ctx *ctx);
 
+/* What one of the library's TMA / tcgen05 kernels allocates per thread block: the figures Gern's
+ * Allocates(reg, smem) statement carries (include/gern/annotations/stmt.h:113-121; the reference's
+ * lowering never reads it, and its kernels carve shared memory at run time with a bump allocator,
+ * gernels/mm/impl/sh_malloc.h:12-54).  Here every kernel's shared memory is a layout planned at
+ * compile time (1024-byte aligned swizzled tiles, mbarriers, TMEM slot) and this call reports it.
+ * Kernel names: "gemm_bf16_tc", "gemm_bf16_2cta", "attention_bf16", "attention_bf16_split".
+ * Works without a device, except that regs_per_thread is then -1. */
+typedef struct gb200_kernel_resources {
+    int regs_per_thread;     /* as compiled; -1 when no device is present to ask          */
+    int threads;             /* threads per block                                          */
+    int dynamic_smem_bytes;  /* dynamic shared memory per block                            */
+    int cluster_x;           /* thread blocks per cluster (1 = no cluster, 2 = CTA pair)   */
+    int tmem_columns;        /* tensor-memory columns the block allocates                  */
+} gb200_kernel_resources;
+int gb200_kernel_resources_query(const char *kernel, gb200_kernel_resources *out);
+
 /* ---- matrix multiply ------------------------------------------------------------------ */
 
 /* fp32 C (+)= A * B, all row-major.  A: M x K (lda), B: K x N (ldb), C: M x N (ldc).
@@ -88,6 +104,16 @@ int gb200_gemm_f32(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, 
  * (gernels/mm/gern_annot/functions.h:7-60); the reference has no bf16 leaf. */
 int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                     void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, void *stream);
+
+/* The same GEMM with the thread-block cluster shape chosen by the caller: cluster_x = 1 runs
+ * one CTA per 128 x 256 tile (gemm_bf16_tc kernel), cluster_x = 2 runs CTA pairs on 256 x 256 tiles
+ * with tcgen05 cta_group::2 (gemm_bf16_2cta kernel); anything else is GB200_ERR_UNSUPPORTED.  It is
+ * what a program's pinned cluster dimension steers: the reference reserves the level
+ * (Grid::Level::BLOCK_CLUSTER, include/gern/annotations/grid.h:47-56) but its launch emitter has
+ * no cluster dimension (src/codegen/codegen.cpp:576-611). */
+int gb200_gemm_bf16_cluster(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                            void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int cluster_x,
+                            void *stream);
 
 /* bf16 GEMM whose consumers run in the epilogue, while the fp32 accumulator is still in TMEM /
  * registers: the reference's elementwise and row-reduction leaves

@@ -226,6 +226,36 @@ static void cpuTests() {
         run.compile();
         CHECK(run.kernel() == Runner::Kernel::GemmBF16);
         CHECK(run.launchArgs().at(Grid::CLUSTER_DIM_X) == 2);
+        // the pinned cluster dimension picks the CTA-pair kernel, whose planned layout is reported
+        CHECK(run.clusterX() == 2 && run.kernelName() == "gemm_bf16_2cta" && run.hasResources());
+        CHECK(run.resources().cluster_x == 2 && run.resources().threads == 192 && run.resources().tmem_columns == 512);
+        CHECK(run.resources().dynamic_smem_bytes > 6 * 32 * 1024 && run.resources().dynamic_smem_bytes <= 200 * 1024);
+        {   // cluster of one: the single-CTA kernel and its (different) layout
+            Composable one = {Global((Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(A, B, C)),
+                                     {{Grid::CLUSTER_DIM_X, Variable("c1").bind(1)}})};
+            Runner r1(one);
+            r1.compile();
+            CHECK(r1.clusterX() == 1 && r1.kernelName() == "gemm_bf16_tc" && r1.resources().cluster_x == 1);
+            CHECK(r1.resources().dynamic_smem_bytes != run.resources().dynamic_smem_bytes);
+        }
+        CHECK(throwsUserError([&] {   // no kernel for clusters of 4
+            Composable bad = {Global((Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(A, B, C)),
+                                     {{Grid::CLUSTER_DIM_X, Variable("c4").bind(4)}})};
+            Runner r(bad);
+            r.compile();
+        }));
+        CHECK(throwsUserError([&] {   // less shared memory than the planned layout of the kernel needs
+            Composable bad = {Global((Tile(C["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(A, B, C)),
+                                     {{Grid::CLUSTER_DIM_X, Variable("c2").bind(2)}}, Variable("s").bind(64 * 1024))};
+            Runner r(bad);
+            r.compile();
+        }));
+        CHECK(throwsUserError([] {    // only the bf16 matrix_multiply has a cluster kernel
+            auto p = blurProgram();
+            Composable bad = {Global(p.program, {{Grid::CLUSTER_DIM_X, Variable("c2").bind(2)}})};
+            Runner r(bad);
+            r.compile();
+        }));
         CHECK(Grid::getLevel(Grid::BLOCK_CLUSTER_Y) == Grid::BLOCK_CLUSTER);
         CHECK(Grid::getDim(Grid::BLOCK_CLUSTER_Z) == Grid::CLUSTER_DIM_Z);
         CHECK(throwsUserError([&] {   // blocks cannot be distributed over... a cluster inside a block

@@ -97,12 +97,27 @@ def test_full_size_properties(ctx, oracle):
     assert float((sums - 1).abs().max()) < 2e-5
     assert bool((out >= 0).all())
     assert torch.equal(out.argmax(dim=1), x.argmax(dim=1))
-    # every row against the oracle (a quarter of the rows at a time keeps host memory modest)
+    # Every element, a quarter of the rows at a time (keeps host memory modest).  Against the exact
+    # (fp64) softmax of the same fp32 inputs the bar is 1e-5.  The fp32 oracle follows the reference's
+    # sum_row, a sequential fp32 sum (test/library/matrix/impl/cpu-matrix.h:146-156), whose own
+    # rounding drift over 4096 columns reaches about 2e-5 on the worst of the 65536 rows; the
+    # kernel's tree-shaped sum does not share it, so against the oracle the bar is 1e-5 plus the
+    # oracle's own distance from the exact value on the same rows.
     oracle.set_threads(oracle.max_threads())
+    worst_vs_oracle = 0.0
     for r0 in range(0, rows, rows // 4):
         xs = x[r0:r0 + rows // 4].cpu().numpy()
-        assert rel_err(out[r0:r0 + rows // 4].cpu().numpy(), oracle.softmax_rows(xs)) <= REL_TOL
+        got = out[r0:r0 + rows // 4].cpu().numpy()
+        exact = oracle.softmax_rows_f64(xs)
+        want = oracle.softmax_rows(xs)
+        assert rel_err(got, exact) <= REL_TOL
+        oracle_drift = rel_err(want, exact)
+        vs_oracle = rel_err(got, want)
+        worst_vs_oracle = max(worst_vs_oracle, vs_oracle)
+        assert vs_oracle <= REL_TOL + oracle_drift
+        del exact, want, got
     oracle.set_threads(1)
+    assert worst_vs_oracle <= 5e-5      # absolute ceiling, whatever the drift
 
 
 def test_host_entry_point(ctx, oracle):
