@@ -141,3 +141,50 @@ def test_bf16_matmul_softmax_and_chain_through_gern(tmp_path, oracle, golden, go
     assert res.returncode == 0, res.stderr
     o = pyoracle.bf16_bits_to_f32(np.fromfile(tmp_path / "o.bin", np.uint16).reshape(64, 128))
     assert np.linalg.norm(o - golden["attn_o"]) / np.linalg.norm(golden["attn_o"]) <= 1e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# Pattern substitution: programs written against the reference's OWN annotation headers
+SUBSTITUTE = os.path.join(ROOT, "integration", "_ref", "gern_b200_substitute")
+needs_substitute = pytest.mark.skipif(not os.path.exists(SUBSTITUTE),
+                                      reason="integration/_ref/gern_b200_substitute not built (needs the Gern tree at build time)")
+SUBSTITUTED = {"blur": ("blur3x3", "gb200_host::blur3x3(input, output)"),
+               "mm_cpu": ("matrix_multiply", "gb200_host::matrix_multiply(A, B, C, k_dim)"),
+               "softmax": ("softmax_rows", "gb200_host::softmax_rows(input, output)")}
+
+
+def run_substitute(what, cwd):
+    return subprocess.run([SUBSTITUTE, "--repo", ROOT, what], capture_output=True, text=True, cwd=cwd, timeout=600)
+
+
+@needs_substitute
+@pytest.mark.parametrize("what", sorted(SUBSTITUTED))
+def test_reference_programs_are_rewritten_onto_the_library(tmp_path, what):
+    """The blur program of apps/blur/blur.cpp:46-73, the tiled matmul of test/test-cpu-mm.cpp:13-83 and
+    the five softmax pieces of apps/common/annot/functions.h, built with the reference's own
+    annotation classes, are recognised by gern::b200::substitute(); the rewritten program goes
+    through the unmodified Runner, and its hook is one call into the library."""
+    kernel, call = SUBSTITUTED[what]
+    res = run_substitute(what, tmp_path)
+    assert f"matched: {kernel}" in res.stdout, res.stdout + res.stderr
+    assert f"compiled: /tmp/gern_b200_substituted_{what}.cpp" in res.stdout, res.stderr
+    src = open(f"/tmp/gern_b200_substituted_{what}.cpp").read()
+    assert call in src and "for(" not in src        # one library call, the schedule's loops are gone
+    if have_gpu():
+        assert res.returncode == 0 and "evaluated: result as expected" in res.stdout, res.stderr
+    else:
+        assert res.returncode == 4 and "status -4" in res.stderr and "no CUDA device" in res.stderr
+
+
+@needs_substitute
+def test_programs_without_a_fused_kernel_are_left_alone(tmp_path):
+    res = run_substitute("unmatched", tmp_path)      # blur with stride 5
+    assert res.returncode == 0 and "matched: none" in res.stdout
+
+
+@needs_substitute
+@gpu
+@pytest.mark.parametrize("what", sorted(SUBSTITUTED))
+def test_substituted_programs_evaluate_on_the_gpu(tmp_path, what):
+    res = run_substitute(what, tmp_path)
+    assert res.returncode == 0 and "evaluated: result as expected" in res.stdout, res.stdout + res.stderr
