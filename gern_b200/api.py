@@ -43,6 +43,8 @@ SIGNATURES = {
     "gb200_blur3x3_f32_band": [_vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp],
     "gb200_attention_bf16": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                              ctypes.c_float, _vp],
+    "gb200_attention_bf16_cluster": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
+                                     ctypes.c_float, _int, _vp],
     "gb200_attention_bf16_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                      ctypes.c_float, _vp, _int],
     "gb200_gemm_f32_host": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int],

@@ -37,7 +37,7 @@ constexpr int CHUNK_BYTES = 128 * 128;     // 16 KiB: 128 rows x 64 bf16
 constexpr int KV_SLOTS = 5;                // one ring for K_0 V_0 K_1 V_1 ...
 constexpr int NUM_THREADS = 320;           // 8 softmax warps + MMA warp + TMA warp
 // Q (2 tiles), K/V ring, then barriers and the TMEM slot
-constexpr smem::AttentionLayout kLayout = smem::attention_layout(NUM_THREADS, 0);
+constexpr smem::AttentionLayout kLayout = smem::attention_layout(NUM_THREADS);
 static_assert(smem::AttentionLayout::kTiles == TILES && smem::AttentionLayout::kKvSlots == KV_SLOTS &&
                   smem::AttentionLayout::kTileBytes == TILE_BYTES && kLayout.q.offset == 0 &&
                   kLayout.kv.offset == TILES * TILE_BYTES,
@@ -461,15 +461,13 @@ int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void
                           const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
                           int64_t d, float scale, cudaStream_t stream);
 
-int attention_split_launch(gb200_ctx *ctx, const CUtensorMap &tq, const CUtensorMap &tk, const CUtensorMap &tv,
-                           void *O, int64_t ldo, int64_t nq, int64_t nkv, float scale, cudaStream_t stream);
 
 #ifndef GB200_ATTN_AUTO_PAIR
 #define GB200_ATTN_AUTO_PAIR 0
 #endif
 
-// kernel_choice: 0 = pick, 1 = one CTA per two Q tiles and one softmax thread per row, 2 = CTA pairs
-// (attention_pair.cu), 3 = one CTA per two Q tiles and two softmax threads per row (attention_split.cu).
+// kernel_choice: 0 = pick, 1 = one CTA per two Q tiles, 2 = CTA pairs with two Q tiles per CTA
+// (attention_pair.cu).
 int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                        const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
                        int64_t d, float scale, cudaStream_t stream, int kernel_choice = 0) {
@@ -489,8 +487,6 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     rc = get_tmap_2d(ctx, V, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)d, (uint64_t)nkv,
                      (uint64_t)ldv * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tv);
     if (rc) return rc;
-    if (kernel_choice == 3)
-        return attention_split_launch(ctx, tq, tk, tv, O, ldo, nq, nkv, scale, stream);
     rc = ensure_dynamic_smem(ctx, attention_bf16_kernel, SMEM_BYTES);
     if (rc) return rc;
     const float scale_log2 = scale * 1.4426950408889634f;
@@ -536,6 +532,20 @@ int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void 
     if (rc) return rc < 0 ? rc : GB200_OK;
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
                               static_cast<cudaStream_t>(stream));
+}
+
+int gb200_attention_bf16_cluster(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
+                                 const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
+                                 int64_t nkv, int64_t d, float scale, int cluster_x, void *stream) {
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(cluster_x == 1 || cluster_x == 2, GB200_ERR_UNSUPPORTED,
+                  "the chain has kernels for clusters of 1 and 2 thread blocks (asked for %d)", cluster_x);
+    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
+                              static_cast<cudaStream_t>(stream), cluster_x);
 }
 
 #ifdef GB200_ATTN_TRACE

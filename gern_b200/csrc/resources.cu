@@ -11,7 +11,7 @@ namespace gb200 {
 int kernel_regs_gemm_tc();
 int kernel_regs_gemm_2cta();
 int kernel_regs_attention();
-int kernel_regs_attention_split();
+int kernel_regs_attention_pair();
 }  // namespace gb200
 
 using namespace gb200;
@@ -28,15 +28,15 @@ extern "C" int gb200_kernel_resources_query(const char *kernel, gb200_kernel_res
         *out = {kernel_regs_gemm_2cta(), smem::Gemm2CtaLayout::kThreads, l.dynamic_bytes, smem::Gemm2CtaLayout::kCluster,
                 smem::Gemm2CtaLayout::kTmemColumns};
     } else if (strcmp(kernel, "attention_bf16") == 0) {
-        constexpr smem::AttentionLayout l = smem::attention_layout(320, 0);
+        constexpr smem::AttentionLayout l = smem::attention_layout(320);
         *out = {kernel_regs_attention(), l.threads, l.dynamic_bytes, smem::AttentionLayout::kCluster,
                 smem::AttentionLayout::kTmemColumns};
-    } else if (strcmp(kernel, "attention_bf16_split") == 0) {
-        constexpr smem::AttentionLayout l = smem::attention_layout(640, 1);
-        *out = {kernel_regs_attention_split(), l.threads, l.dynamic_bytes, smem::AttentionLayout::kCluster,
-                smem::AttentionLayout::kTmemColumns};
+    } else if (strcmp(kernel, "attention_bf16_pair") == 0) {
+        constexpr smem::AttentionPairLayout l = smem::attention_pair_layout();
+        *out = {kernel_regs_attention_pair(), smem::AttentionPairLayout::kThreads, l.dynamic_bytes,
+                smem::AttentionPairLayout::kCluster, smem::AttentionPairLayout::kTmemColumns};
     } else {
-        set_error("no kernel named '%s' (known: gemm_bf16_tc, gemm_bf16_2cta, attention_bf16, attention_bf16_split)",
+        set_error("no kernel named '%s' (known: gemm_bf16_tc, gemm_bf16_2cta, attention_bf16, attention_bf16_pair)",
                   kernel);
         return GB200_ERR_INVALID_ARG;
     }

@@ -96,15 +96,13 @@ constexpr Gemm2CtaLayout gemm_2cta_layout(int stages_n) {
 }
 
 // ---- GEMM -> softmax -> GEMM, two Q tiles per CTA -----------------------------------------------
-// `row_words` words per Q row follow the barriers (the running-maximum exchange of the kernel with
-// two softmax threads per row; 0 for the kernel with one).
 struct AttentionLayout {
     static constexpr int kTiles = 2, kKvSlots = 5, kTileBytes = 128 * 128 * 2, kTmemColumns = 512, kCluster = 1;
     int threads = 320;
-    Region q, kv, q_full, kv_full, kv_empty, s_full, sp_ready, o_full, p_half, tmem_slot, row_words;
+    Region q, kv, q_full, kv_full, kv_empty, s_full, sp_ready, o_full, p_half, tmem_slot;
     int dynamic_bytes = 0;
 };
-constexpr AttentionLayout attention_layout(int threads, int row_words) {
+constexpr AttentionLayout attention_layout(int threads) {
     AttentionLayout l;
     Planner p;
     l.threads = threads;
@@ -118,16 +116,41 @@ constexpr AttentionLayout attention_layout(int threads, int row_words) {
     l.o_full = p.barriers(AttentionLayout::kTiles);
     l.p_half = p.barriers(AttentionLayout::kTiles);
     l.tmem_slot = p.words(1);
-    l.row_words = p.take(row_words * AttentionLayout::kTiles * 128 * 4, 16);
     l.dynamic_bytes = p.dynamic_bytes();
     return l;
 }
 
+// ---- GEMM -> softmax -> GEMM on CTA pairs, two Q tiles per CTA ------------------------------------
+// Each CTA holds its two Q tiles and a ring of half blocks: 64 kv rows of K_j, or 64 head-dimension
+// columns of V_j (16 KiB each).
+struct AttentionPairLayout {
+    static constexpr int kTiles = 2, kKvSlots = 10, kTileBytes = 128 * 128 * 2, kHalfBytes = 16 * 1024,
+                         kThreads = 320, kTmemColumns = 512, kCluster = 2;
+    Region q, kv, q_full, kv_full, kv_empty, s_full, sp_ready, o_full, p_half, tmem_slot;
+    int dynamic_bytes = 0;
+};
+constexpr AttentionPairLayout attention_pair_layout() {
+    AttentionPairLayout l;
+    Planner p;
+    l.q = p.tiles(AttentionPairLayout::kTiles, AttentionPairLayout::kTileBytes);
+    l.kv = p.tiles(AttentionPairLayout::kKvSlots, AttentionPairLayout::kHalfBytes);
+    l.q_full = p.barriers(1);
+    l.kv_full = p.barriers(AttentionPairLayout::kKvSlots);
+    l.kv_empty = p.barriers(AttentionPairLayout::kKvSlots);
+    l.s_full = p.barriers(AttentionPairLayout::kTiles);
+    l.sp_ready = p.barriers(AttentionPairLayout::kTiles);
+    l.o_full = p.barriers(AttentionPairLayout::kTiles);
+    l.p_half = p.barriers(AttentionPairLayout::kTiles);
+    l.tmem_slot = p.words(1);
+    l.dynamic_bytes = p.dynamic_bytes();
+    return l;
+}
+static_assert(attention_pair_layout().dynamic_bytes <= kMaxDynamicBytes, "pair attention layout exceeds a block's shared memory");
+
 static_assert(gemm_tc_layout(256).dynamic_bytes <= kMaxDynamicBytes, "GEMM ring exceeds a block's shared memory");
 static_assert(gemm_2cta_layout(6).dynamic_bytes <= kMaxDynamicBytes, "pair GEMM ring exceeds a block's shared memory");
-static_assert(attention_layout(320, 0).dynamic_bytes <= kMaxDynamicBytes, "attention layout exceeds a block's shared memory");
-static_assert(attention_layout(640, 1).dynamic_bytes <= kMaxDynamicBytes, "attention layout exceeds a block's shared memory");
-static_assert(gemm_tc_layout(192).stages.offset % kSwizzleTileAlign == 0 && attention_layout(640, 1).kv.offset % kSwizzleTileAlign == 0,
+static_assert(attention_layout(320).dynamic_bytes <= kMaxDynamicBytes, "attention layout exceeds a block's shared memory");
+static_assert(gemm_tc_layout(192).stages.offset % kSwizzleTileAlign == 0 && attention_layout(320).kv.offset % kSwizzleTileAlign == 0,
               "swizzled tiles start on 1024-byte boundaries");
 
 }  // namespace smem

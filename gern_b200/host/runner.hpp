@@ -129,8 +129,12 @@ public:
             case Kernel::Attention: {
                 auto &Q = M(names[0]), &K = M(names[1]), &V = M(names[2]), &O = M(names[3]);
                 require(Q.col == K.col && K.row == V.row && O.row == Q.row && O.col == V.col, "attention: shapes do not agree");
-                rc = gb200_attention_bf16(ctx, Q.data, Q.lda, K.data, K.lda, V.data, V.lda, O.data, O.lda,
-                                          Q.row, K.row, Q.col, scale, stream);
+                if (cluster_x > 0)
+                    rc = gb200_attention_bf16_cluster(ctx, Q.data, Q.lda, K.data, K.lda, V.data, V.lda, O.data, O.lda,
+                                                      Q.row, K.row, Q.col, scale, cluster_x, stream);
+                else
+                    rc = gb200_attention_bf16(ctx, Q.data, Q.lda, K.data, K.lda, V.data, V.lda, O.data, O.lda,
+                                              Q.row, K.row, Q.col, scale, stream);
                 break;
             }
             case Kernel::GemmEpilogue: {
@@ -232,7 +236,8 @@ private:
     }
 
     // Turns what Global() pinned into the launch: the cluster dimension picks between the kernels
-    // the library has for the planned operator, and the program's shared-memory request is held
+    // the library has for the planned operator (bf16 matrix_multiply and the fused chain have one for
+    // single CTAs and one for CTA pairs), and the program's shared-memory request is held
     // against the planned layout of that kernel.
     void bindLaunch() {
         cluster_x = 0;
@@ -253,12 +258,17 @@ private:
                 kernel_name = cluster_x == 1 ? "gemm_bf16_tc" : "gemm_bf16_2cta";
                 break;
             case Kernel::GemmEpilogue: kernel_name = "gemm_bf16_tc"; break;
-            case Kernel::Attention: kernel_name = "attention_bf16"; break;
+            case Kernel::Attention:
+                if (cluster_x != 0 && cluster_x != 1 && cluster_x != 2)
+                    throw error::UserError("Global: the fused chain has kernels for clusters of 1 and 2 thread "
+                                           "blocks, not " + std::to_string(cluster_x));
+                kernel_name = cluster_x == 2 ? "attention_bf16_pair" : "attention_bf16";
+                break;
             default: break;
         }
-        if (plan != Kernel::GemmBF16 && cluster_x > 1)
-            throw error::UserError("Global: only the bf16 matrix_multiply has a kernel for clusters of " +
-                                   std::to_string(cluster_x) + " thread blocks");
+        if (plan != Kernel::GemmBF16 && plan != Kernel::Attention && cluster_x > 1)
+            throw error::UserError("Global: only the bf16 matrix_multiply and the fused chain have kernels for "
+                                   "clusters of " + std::to_string(cluster_x) + " thread blocks");
         if (kernel_name.empty()) return;
         if (gb200_kernel_resources_query(kernel_name.c_str(), &kernel_resources) != 0)
             throw error::InternalError(std::string("libgern_b200: ") + gb200_last_error_string());

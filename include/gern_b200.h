@@ -73,7 +73,7 @@ int64_t gb200_launch_count(gb200_ctx *ctx);
  * lowering never reads it, and its kernels carve shared memory at run time with a bump allocator,
  * gernels/mm/impl/sh_malloc.h:12-54).  Here every kernel's shared memory is a layout planned at
  * compile time (1024-byte aligned swizzled tiles, mbarriers, TMEM slot) and this call reports it.
- * Kernel names: "gemm_bf16_tc", "gemm_bf16_2cta", "attention_bf16", "attention_bf16_split".
+ * Kernel names: "gemm_bf16_tc", "gemm_bf16_2cta", "attention_bf16", "attention_bf16_pair".
  * Works without a device, except that regs_per_thread is then -1. */
 typedef struct gb200_kernel_resources {
     int regs_per_thread;     /* as compiled; -1 when no device is present to ask          */
@@ -203,6 +203,14 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
 int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                          int64_t nkv, int64_t d, float scale, void *stream);
+
+/* The same chain with the thread-block cluster shape chosen by the caller: cluster_x = 1 runs one CTA
+ * per two 128-row Q tiles, cluster_x = 2 runs CTA pairs that share every MMA (tcgen05 cta_group::2:
+ * each CTA holds half of every K and V block); anything else is GB200_ERR_UNSUPPORTED.  Results are
+ * identical bit for bit.  See gb200_gemm_bf16_cluster for what this stands for in the reference. */
+int gb200_attention_bf16_cluster(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
+                                 const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
+                                 int64_t nkv, int64_t d, float scale, int cluster_x, void *stream);
 
 /* ---- single-process multi-GPU forms ---------------------------------------------------- */
 

@@ -250,9 +250,12 @@ static void cpuTests() {
             Runner r(bad);
             r.compile();
         }));
-        CHECK(throwsUserError([] {    // only the bf16 matrix_multiply has a cluster kernel
-            auto p = blurProgram();
-            Composable bad = {Global(p.program, {{Grid::CLUSTER_DIM_X, Variable("c2").bind(2)}})};
+        CHECK(throwsUserError([&] {   // the fp32 matrix_multiply has no cluster kernel
+            auto fA = AbstractDataTypePtr(new const annot::MatrixGPU("A"));
+            auto fB = AbstractDataTypePtr(new const annot::MatrixGPU("B"));
+            auto fC = AbstractDataTypePtr(new const annot::MatrixGPU("C"));
+            Composable bad = {Global((Tile(fC["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(fA, fB, fC)),
+                                     {{Grid::CLUSTER_DIM_X, Variable("c2").bind(2)}})};
             Runner r(bad);
             r.compile();
         }));
@@ -467,6 +470,22 @@ static void gpuTests() {
                 exact = exact && fl(hc[i * n + j]) == sum;
             }
         CHECK(exact);
+        // Global({{CLUSTER_DIM_X, c}}) steers the launch: c = 1 the single-CTA kernel, c = 2 CTA pairs;
+        // both produce the same exact product
+        for (int64_t c : {1, 2}) {
+            Variable bx("bx"), cx("cx");
+            annot::MatrixMultiply mm;
+            Composable pinned = {Global((Tile(p.C["row"], bx.bind(128)) || Grid::BLOCK_X)(mm(p.A, p.B, p.C)),
+                                        {{Grid::CLUSTER_DIM_X, cx.bind(c)}})};
+            Runner rc(pinned);
+            rc.compile();
+            CHECK(rc.clusterX() == c && rc.resources().cluster_x == c);
+            std::vector<uint16_t> hz(m * n, 0x7fc0), hc2(m * n);
+            C.put_raw(hz.data());
+            rc.evaluate({{"A", &A}, {"B", &B}, {"C", &C}});
+            C.get_raw(hc2.data());
+            CHECK(hc2 == hc);
+        }
         A.destroy(); B.destroy(); C.destroy();
     }
     {   // exp(0.25 * A B - m) with row sums, against a CPU loop on the same small integers
@@ -523,6 +542,17 @@ static void gpuTests() {
         bool ok = true;
         for (int64_t i = 0; i < nq * d; i++) ok = ok && std::fabs(fl(ho[i]) - 1.5f) < 0.02f;
         CHECK(ok);
+        {   // the same chain pinned to CTA pairs: the kernel for clusters of two, same bits
+            Composable pinned = {Global(p.program.get()->children[0], {{Grid::CLUSTER_DIM_X, Variable("cx").bind(2)}})};
+            Runner rp(pinned);
+            rp.compile();
+            CHECK(rp.kernelName() == "attention_bf16_pair" && rp.resources().cluster_x == 2);
+            std::vector<uint16_t> ho2(nq * d, 0);
+            O.put_raw(ho2.data());
+            rp.evaluate({{"Q", &Q}, {"K", &K}, {"V", &V}, {"O", &O}});
+            O.get_raw(ho2.data());
+            CHECK(ho2 == ho);
+        }
         Q.destroy(); K.destroy(); V.destroy(); O.destroy();
     }
 }

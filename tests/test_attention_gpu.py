@@ -36,11 +36,11 @@ def test_against_oracle(ctx, oracle, nq, nkv):
     assert frob(o.float().cpu().numpy(), want) <= 1e-2
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
-@pytest.mark.parametrize("nq,nkv", [(256, 128), (256, 1024), (100, 200), (130, 129), (1, 1), (640, 2048), (300, 190)])
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("nq,nkv", [(256, 128), (256, 1024), (100, 200), (130, 129), (1, 1), (640, 2048), (300, 190),
+                                    (512, 384), (1100, 700)])
 def test_kernel_variants(ctx, oracle, nq, nkv, variant):
-    """Two-tile kernel with one softmax thread per row (1), CTA-pair kernel (2) and two-tile kernel
-    with two softmax threads per row (3), forced."""
+    """One CTA per two Q tiles (1) and CTA pairs with two Q tiles per CTA (2), forced."""
     q, k, v = make(nq, nkv, nq * 7 + nkv)
     o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
     scale = 1.0 / np.sqrt(128.0)
@@ -64,7 +64,7 @@ def test_pair_kernel_rescale_path(ctx, oracle):
     assert frob(o.float().cpu().numpy(), want) <= 1e-2
 
 
-@pytest.mark.parametrize("variant", [None, 1, 3])
+@pytest.mark.parametrize("variant", [None, 1, 2])
 def test_peaked_rows_exercise_the_rescale(ctx, oracle, variant):
     """Large logits whose maximum keeps growing along kv force the running-max correction."""
     nq, nkv = 256, 1024
@@ -102,7 +102,7 @@ def test_against_reference_chain_fixture(ctx, golden, golden_maker):
     subtract_vec -> exp_matrix -> sum_row -> divide_vec -> matrix_multiply
     (test/library/matrix/impl/cpu-matrix.h:134-212) on the same bf16-rounded Q, K, V."""
     q, k, v = (torch.from_numpy(t.view(np.int16)).cuda().view(torch.bfloat16) for t in golden_maker.bf16_inputs("attn"))
-    for variant in (None, 1, 2, 3):
+    for variant in (None, 1, 2):
         o = torch.zeros((q.shape[0], 128), dtype=torch.bfloat16, device="cuda")
         ctx.attention_bf16(q, k, v, o, golden_maker.ATTN_SCALE, variant=variant)
         ctx.sync()
