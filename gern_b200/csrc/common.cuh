@@ -223,8 +223,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait.  Returns false (after writing `code` to *status) if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
+// Bounded wait.  Returns false (after writing `code` to *status) if `limit_ns` of wall-clock time
+// ran out (on top of the clock-free polls of the fast path, at most about 20 ms).
+__device__ __forceinline__ bool mbar_wait_ns(uint64_t *bar, uint32_t parity, int *status, int code,
+                                             unsigned long long limit_ns) {
     // Fast path: polls without a clock.  Reading the wall-clock timer is a long-latency operation
     // (a barrier that completes while the read is outstanding is noticed late, which showed as
     // microseconds on the TMA -> MMA -> epilogue hand-offs of a short GEMM), so the timer is
@@ -236,10 +238,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *s
     while (true) {
         for (int i = 0; i < 32; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        if (global_timer_ns() - t0 > limit_ns) break;
     }
     if (status) atomicExch(status, code);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
+    return mbar_wait_ns(bar, parity, status, code, kWaitLimitNs);
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -131,11 +131,37 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
     return GB200_OK;
 }
 
+// Self-test of the bounded wait every TMA / tcgen05 kernel relies on: one thread waits on an mbarrier
+// that nobody ever arrives on, with the wall-clock limit given by the caller.  The wait gives up,
+// records code 901 in the status word and the kernel returns: nothing hangs and nothing faults.
+__global__ void bounded_wait_probe_kernel(int *status, unsigned long long limit_ns, int *returned) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+        const bool completed = mbar_wait_ns(&bar, 0, status, 901, limit_ns);
+        *returned = completed ? 2 : 1;
+    }
+}
+
 }  // namespace gb200
 
 using namespace gb200;
 
 extern "C" {
+
+// Test hook (not part of the documented surface): launches the probe above on `stream`.
+// `returned` is a device int that the kernel sets to 1 when the wait gave up (2 if it completed).
+int gb200_selftest_bounded_wait(gb200_ctx *ctx, unsigned long long limit_ns, int *returned, void *stream) {
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(returned != nullptr, GB200_ERR_INVALID_ARG, "returned is NULL");
+    GB200_REQUIRE(limit_ns <= 100ull * 1000ull * 1000ull, GB200_ERR_INVALID_ARG,
+                  "the probe's limit is capped at 100 ms");
+    bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctx->d_status, limit_ns, returned);
+    return after_launch(ctx, "bounded_wait_probe_kernel");
+}
 
 const char *gb200_last_error_string(void) { return g_err; }
 
