@@ -241,8 +241,11 @@ class BlurWorkload(Workload):
                 if self.band.recvs_halo:
                     peer = hdl.get_buffer(rank + 1, (cap, n), torch.float32)
                     self.halo = peer[0:2]
-                self._symm = (buf, hdl)
                 self.transport = "peer loads over NVLink (symmetric memory)"
+                self._symm = (buf, hdl)
+                # every band is complete before any rank's kernel may read a neighbour's rows
+                torch.cuda.synchronize()
+                dist.barrier()
             except Exception as e:  # noqa: BLE001
                 self.transport = f"NCCL send/recv ({type(e).__name__})"
                 self.x = torch.rand((rows, n), generator=g, device="cuda")
