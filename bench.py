@@ -518,6 +518,53 @@ class GemmBf16Workload(Workload):
         return 2.0 * rows * self.N * self.N / dt / 1e12, f"{rows} rows of C (M-panel of {rows} x {self.N} x {self.N})"
 
 
+class GemmEpilogueWorkload(GemmBf16Workload):
+    """The bf16 GEMM with consumers fused into its epilogue (gb200_gemm_bf16_epilogue): E = exp(A B - sub)
+    stored as bf16 plus the row sums of E, the shape of a softmax numerator.  A side measurement
+    beside the plain GEMM (same operands, same FLOP count; the consumers add 67 M exponentials)."""
+    name = "gemm_epilogue"
+    metric = "bf16 GEMM with exp and row-sum consumers in the epilogue, dense FLOP per second"
+    kernel = "gemm_bf16_2cta_kernel<epilogue>"
+    sharded = False
+    VARIANT = None      # --variant 1: single-CTA tiles, 2: CTA pairs (default: the library picks)
+
+    def __init__(self, ctx, rank, world, torch, dist=None, mode="single"):
+        super().__init__(ctx, rank, world, torch, dist, mode)
+        m = self.mnk[0]
+        self.sub = torch.full((m,), 0.25, device="cuda")
+        self.row_sum = torch.empty((m,), device="cuda")
+
+    def step(self, stream):
+        self.ctx.gemm_bf16_epilogue(self.a, self.b, self.c, alpha=1.0, row_sub=self.sub, apply_exp=True,
+                                    row_sum=self.row_sum, stream=stream, variant=self.VARIANT)
+
+    def launches_note(self):
+        return "two launches per step: the row-sum vector is initialised by a small kernel"
+
+    def parity(self, oracle):
+        torch = self.torch
+        idx = spread_rows(self.mnk[0], 64)
+        sel = torch.tensor(idx, device="cuda")
+        t, _, rs = oracle.gemm_bf16_epilogue(bits_of(self.a[sel], torch), bits_of(self.b, torch), alpha=1.0,
+                                             row_sub=np.full(len(idx), 0.25, np.float32), apply_exp=True)
+        got = self.c[sel].float().cpu().numpy()
+        err = float(np.linalg.norm(got - t) / max(np.linalg.norm(t), 1e-30))
+        rel = float(np.abs(self.row_sum[sel].cpu().numpy() - rs).max() / np.abs(rs).max())
+        ok = err <= 1e-2 and rel <= 1e-3
+        return len(idx), ok, "" if ok else f"gemm_epilogue: C rel Frobenius {err:.3g}, row sums {rel:.3g}"
+
+    def e2e_setup(self):
+        return 0, 0
+
+    def config(self):
+        m, n, k = self.mnk
+        return {"workload": f"bf16 GEMM M={m} N={n} K={k} with E = exp(A B - sub) stored as bf16 and row sums of E (fused consumers)",
+                "sharding": "replicas only", "cache": "flush not needed: 384 MB of operands > L2"}
+
+    def cpu_sample(self, oracle, ref):
+        return 0.0, "none"
+
+
 class AttentionWorkload(Workload):
     name = "attention"
     metric = "GEMM->softmax->GEMM chain, dense FLOP per second"
@@ -727,7 +774,7 @@ class GemmF32Workload(Workload):
 
 
 WORKLOADS = {w.name: w for w in (BlurWorkload, SoftmaxWorkload, GemmBf16Workload, AttentionWorkload,
-                                 GemmF32Workload, GemmF32ShapeWorkload)}
+                                 GemmF32Workload, GemmF32ShapeWorkload, GemmEpilogueWorkload)}
 
 
 HOST_ENTRY = {"blur": "gb200_blur3x3_f32_host", "softmax": "gb200_softmax_rows_f32_host",
@@ -861,7 +908,8 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="reduced sizes (still larger than L2) for profiler captures; not a bench number")
     ap.add_argument("--variant", type=int, default=None,
-                    help="blur only, one GPU: kernel variant of gb200_blur3x3_f32_variant (52 = TMA-staged, short strips)")
+                    help="blur, one GPU: kernel variant of gb200_blur3x3_f32_variant (52 = TMA-staged, short strips); "
+                         "gemm_epilogue: 1 = single-CTA tiles, 2 = CTA pairs")
     ap.add_argument("--shape", default="", help="gemm_bf16 / gemm_f32: M,N,K of a side measurement (kernel only)")
     ap.add_argument("--vs-cublas", action="store_true",
                     help="with --shape: add cuBLAS (torch.matmul) timed the same way under 'library'")
@@ -907,10 +955,16 @@ def main():
             dist.all_reduce(t, op=getattr(dist.ReduceOp, op))
         return float(t.item())
 
-    if args.variant is not None:
+    if args.variant is not None and args.workload == "gemm_epilogue":
+        GemmEpilogueWorkload.VARIANT = args.variant
+        if args.variant == 1:
+            GemmEpilogueWorkload.kernel = "gemm_bf16_tc_kernel<epilogue>"
+    elif args.variant is not None:
         BlurWorkload.VARIANT = args.variant
         if 2 <= args.variant < 40 or args.variant >= 50:
             BlurWorkload.kernel = "blur3x3_tma_kernel"
+    if args.workload == "gemm_epilogue":
+        args.no_e2e = args.no_cpu_baseline = True
     if args.shape:
         GemmBf16Workload.SHAPE = tuple(int(v) for v in args.shape.split(","))
         GemmF32ShapeWorkload.SHAPE = GemmBf16Workload.SHAPE
@@ -1050,14 +1104,15 @@ def main():
 
     def strong_with_reference(name, steps, warmup):
         """The one configuration cut `world` ways, beside the same problem on rank 0 alone."""
-        t1 = 0.0
-        if rank == 0:
-            solo = WORKLOADS[name](ctx, 0, 1, torch, None, "single")
-            _, t1, _ = timed_loop(solo, steps, warmup, group=False)
-            del solo
-            torch.cuda.empty_cache()
+        # Every rank runs the whole problem by itself first (rank 0's time is the one reported): the
+        # ranks then enter the strong-scaled run in the same thermal and power state.  With rank 0
+        # alone doing the 40 ms of full-size GEMMs, its panel ran a third slower than the others'.
+        solo = WORKLOADS[name](ctx, 0, 1, torch, None, "single")
+        _, t1, _ = timed_loop(solo, steps, warmup, group=False)
+        del solo
+        torch.cuda.empty_cache()
         barrier()
-        t1 = allreduce(t1, "MAX")
+        t1 = allreduce(t1 if rank == 0 else 0.0, "MAX")
         r = run_workload(name, "strong", steps, warmup, False, False)
         r["one_gpu_ms_per_step"] = t1
         r["speedup_vs_one_gpu"] = t1 / r["ms_per_step"]

@@ -97,6 +97,8 @@ class GemmEpilogue(ctypes.Structure):
 lib.gb200_gemm_bf16_epilogue.argtypes = [_vp, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                          ctypes.POINTER(GemmEpilogue), _vp]
 lib.gb200_gemm_bf16_epilogue.restype = _int
+lib.gb200_gemm_bf16_epilogue_variant.argtypes = lib.gb200_gemm_bf16_epilogue.argtypes + [_int]
+lib.gb200_gemm_bf16_epilogue_variant.restype = _int
 SIGNATURES["gb200_gemm_bf16_epilogue"] = None
 
 
@@ -268,12 +270,17 @@ class Context:
                                    K, _stream(stream)), "gb200_gemm_bf16")
 
     def gemm_bf16_epilogue(self, A, Bt, C=None, alpha=1.0, row_sub=None, apply_exp=False, row_div=None,
-                           row_max=None, row_sum=None, stream=None):
+                           row_max=None, row_sum=None, stream=None, variant=None):
         """C = bf16(epilogue(alpha * A Bt^T)); any of C / row_max / row_sum may be left out."""
         M, K = A.shape
         N = Bt.shape[0]
         e = GemmEpilogue(ctypes.c_float(alpha), _ptr(row_sub), int(bool(apply_exp)), _ptr(row_div),
                          _ptr(row_max), _ptr(row_sum))
+        if variant is not None:
+            _check(lib.gb200_gemm_bf16_epilogue_variant(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C),
+                                                        _ld(C) if C is not None else 0, M, N, K, ctypes.byref(e),
+                                                        _stream(stream), int(variant)), "gb200_gemm_bf16_epilogue_variant")
+            return
         _check(lib.gb200_gemm_bf16_epilogue(self.handle, _ptr(A), _ld(A), _ptr(Bt), _ld(Bt), _ptr(C),
                                             _ld(C) if C is not None else 0, M, N, K, ctypes.byref(e),
                                             _stream(stream)), "gb200_gemm_bf16_epilogue")

@@ -533,6 +533,15 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     return d;
 }
 
+// max over floats with integer atomics: non-negative values order like signed integers,
+// negative ones like unsigned integers in reverse; the target starts at -inf.
+__device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
+    if (v >= 0.0f)
+        atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
+    else
+        atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
     asm volatile(

@@ -77,14 +77,6 @@ struct GemmEpi {
     int seg_kb;
 };
 
-// max over floats with integer atomics: non-negative values order like signed integers,
-// negative ones like unsigned integers in reverse; the target starts at -inf.
-__device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
-    if (v >= 0.0f)
-        atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
-    else
-        atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
-}
 
 __global__ void epilogue_init_kernel(float *row_max, float *row_sum, int M) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -583,9 +575,14 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
 
 // GEMM with consumers fused into the epilogue (single-CTA tiles, no split-K: the reductions and
 // the exponential need the complete dot product).
+int gemm_bf16_2cta_epilogue_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                                   void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha,
+                                   const float *row_sub, int apply_exp, const float *row_div, float *row_max,
+                                   float *row_sum, cudaStream_t stream);
+
 int gemm_bf16_epilogue_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B,
                                 int64_t ldb, void *C, int64_t ldc, int64_t M, int64_t N, int64_t K,
-                                const GemmEpi &epi, cudaStream_t stream) {
+                                const GemmEpi &epi, cudaStream_t stream, int kernel_choice = 0) {
     using namespace gemm;
     auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     GB200_REQUIRE(ctx->encode_tiled != nullptr, GB200_ERR_NO_DEVICE, "TMA descriptors unavailable");
@@ -596,6 +593,12 @@ int gemm_bf16_epilogue_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, cons
         int rc0 = after_launch(ctx, "epilogue_init_kernel");
         if (rc0) return rc0;
     }
+    // CTA-pair tiles when there are enough of them to fill the SM pairs, as for the plain GEMM
+    // (kernel_choice: 0 = pick, 1 = single-CTA tiles, 2 = CTA pairs)
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    if (kernel_choice == 2 || (kernel_choice == 0 && GB200_GEMM_AUTO_PAIR && pair_tiles >= ctx->sm_count / 2))
+        return gemm_bf16_2cta_epilogue_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, epi.alpha, epi.row_sub,
+                                              epi.apply_exp, epi.row_div, epi.row_max, epi.row_sum, stream);
     CUtensorMap ta, tb;
     int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                          (uint64_t)lda * 2, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
@@ -647,6 +650,35 @@ int gb200_gemm_bf16_epilogue(gb200_ctx *ctx, const void *A, int64_t lda, const v
     epi.apply_exp = e->apply_exp;
     return gemm_bf16_epilogue_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, epi,
                                        static_cast<cudaStream_t>(stream));
+}
+
+// Test / benchmark hook: kernel chosen by the caller (1 = single-CTA tiles, 2 = CTA pairs).
+int gb200_gemm_bf16_epilogue_variant(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                                     void *C, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                                     const gb200_gemm_epilogue *e, void *stream, int variant) {
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(e != nullptr, GB200_ERR_INVALID_ARG, "epilogue description is NULL");
+    GB200_REQUIRE(C != nullptr || e->row_max != nullptr || e->row_sum != nullptr, GB200_ERR_INVALID_ARG,
+                  "nothing to produce: C, row_max and row_sum are all NULL");
+    GB200_REQUIRE(M >= 0 && N >= 0 && K >= 0, GB200_ERR_INVALID_ARG, "negative extent");
+    GB200_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), GB200_ERR_UNSUPPORTED,
+                  "extent beyond 2^31");
+    if (M == 0 || N == 0) return GB200_OK;
+    GB200_REQUIRE(K > 0, GB200_ERR_UNSUPPORTED, "gemm epilogue: K must be positive");
+    GB200_REQUIRE(A != nullptr && B != nullptr, GB200_ERR_INVALID_ARG, "NULL matrix pointer");
+    GB200_REQUIRE(lda >= K && ldb >= K && (C == nullptr || ldc >= N), GB200_ERR_INVALID_ARG,
+                  "leading dimension smaller than the row");
+    GemmEpi epi{};
+    epi.alpha = e->alpha;
+    epi.row_sub = e->row_sub;
+    epi.row_div = e->row_div;
+    epi.row_max = e->row_max;
+    epi.row_sum = e->row_sum;
+    epi.apply_exp = e->apply_exp;
+    return gemm_bf16_epilogue_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, epi,
+                                       static_cast<cudaStream_t>(stream), variant);
 }
 
 int gb200_gemm_bf16(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,

@@ -54,14 +54,25 @@ struct Gemm2F32 {
     int64_t ldc32;
     int accumulate;
     int seg_kb;
+    // consumers fused into the epilogue (MODE 2), as in the single-CTA kernel of gemm_bf16.cu:
+    // t = alpha * acc; t -= row_sub[i]; t = exp(t); t /= row_div[i]; then bf16 C, row maxima, row sums
+    float alpha;
+    const float *row_sub;
+    const float *row_div;
+    float *row_max;
+    float *row_sum;
+    int apply_exp;
 };
 
-template <bool F32X3>
+// MODE 0: bf16 C = A B.  MODE 1: fp32 C from three-way bf16 splits.  MODE 2: bf16 C with consumers.
+template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::NUM_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
                       int64_t ldc, int M, int N, int K, int *status, Gemm2F32 f32) {
     using namespace gemm2;
+    constexpr bool F32X3 = MODE == 1;
+    constexpr bool EPI = MODE == 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -182,13 +193,33 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int row = tm * BM + (int)rank * HALF + lane_group * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                    static_cast<uint32_t>(buf * BN);
+            float e_sub = 0.0f, e_inv = 1.0f, e_max = -INFINITY, e_sum = 0.0f;
+            if (EPI && row < M) {
+                if (f32.row_sub) e_sub = f32.row_sub[row];
+                if (f32.row_div) e_inv = 1.0f / f32.row_div[row];
+            }
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + ch * 32, r);
                 tmem_ld_wait();
                 const int col = tn * BN + ch * 32;
-                if (F32X3) {
+                if (EPI) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float v = fmaf(__uint_as_float(r[j]), f32.alpha, -e_sub);
+                        if (f32.apply_exp) v = __expf(v);
+                        v *= e_inv;
+                        r[j] = __float_as_uint(v);
+                        if (col + j < N) {
+                            e_max = fmaxf(e_max, v);
+                            e_sum += v;
+                        }
+                    }
+                }
+                if (EPI && C == nullptr) {
+                    // reductions only: the product itself is a temporary that is never stored
+                } else if (F32X3) {
                     if (row < M && col < N) {
                         float *dst = f32.c32 + static_cast<int64_t>(row) * f32.ldc32 + col;
                         const bool v4 = (f32.ldc32 % 4 == 0) &&
@@ -241,6 +272,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     }
                 }
             }
+            if (EPI && row < M) {
+                // one atomic per row and 256-column tile; the vectors were initialised by the host side
+                if (f32.row_max) atomic_max_f32(f32.row_max + row, e_max);
+                if (f32.row_sum) atomicAdd(f32.row_sum + row, e_sum);
+            }
             tc_fence_before();
             __syncwarp();
             // the accumulator buffer is free once both CTAs have drained their halves
@@ -271,9 +307,9 @@ int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int64_t pairs = ctx->sm_count / 2;
     if (pairs > n_tiles) pairs = n_tiles;
-    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<false>, SMEM_BYTES);
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<0>, SMEM_BYTES);
     if (rc) return rc;
-    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<false>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<0>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                               (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
                               (int)N, (int)K, ctx->d_status, Gemm2F32{}));
     return after_launch(ctx, "gemm_bf16_2cta_kernel");
@@ -294,19 +330,50 @@ int gemm_f32x3_2cta_launch(gb200_ctx *ctx, const void *A3, const void *B3, float
     const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     int64_t pairs = ctx->sm_count / 2;
     if (pairs > n_tiles) pairs = n_tiles;
-    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<true>, SMEM_BYTES);
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<1>, SMEM_BYTES);
     if (rc) return rc;
-    Gemm2F32 f32;
+    Gemm2F32 f32{};
     f32.c32 = C;
     f32.ldc32 = ldc;
     f32.accumulate = accumulate;
     f32.seg_kb = (int)(Kp / BK);
-    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<true>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<1>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                               (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(nullptr),
                               (int64_t)0, (int)M, (int)N, (int)(6 * Kp), ctx->d_status, f32));
     return after_launch(ctx, "gemm_bf16_2cta_kernel<f32x3>");
 }
 
-int kernel_regs_gemm_2cta() { return kernel_registers(gemm_bf16_2cta_kernel<false>); }
+// bf16 GEMM with consumers in the epilogue on CTA pairs; the caller has initialised row_max / row_sum.
+int gemm_bf16_2cta_epilogue_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
+                                   void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha,
+                                   const float *row_sub, int apply_exp, const float *row_div, float *row_max,
+                                   float *row_sum, cudaStream_t stream) {
+    using namespace gemm2;
+    CUtensorMap ta, tb;
+    int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
+                         (uint64_t)lda * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
+    if (rc) return rc;
+    rc = get_tmap_2d(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
+                     (uint64_t)ldb * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+    if (rc) return rc;
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    int64_t pairs = ctx->sm_count / 2;
+    if (pairs > n_tiles) pairs = n_tiles;
+    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<2>, SMEM_BYTES);
+    if (rc) return rc;
+    Gemm2F32 e{};
+    e.alpha = alpha;
+    e.row_sub = row_sub;
+    e.row_div = row_div;
+    e.row_max = row_max;
+    e.row_sum = row_sum;
+    e.apply_exp = apply_exp;
+    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<2>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+                              (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
+                              (int)N, (int)K, ctx->d_status, e));
+    return after_launch(ctx, "gemm_bf16_2cta_kernel<epilogue>");
+}
+
+int kernel_regs_gemm_2cta() { return kernel_registers(gemm_bf16_2cta_kernel<0>); }
 
 }  // namespace gb200

@@ -28,7 +28,7 @@ def operands(M, N, K, seed, std=0.25):
 
 
 def run(ctx, oracle, M, N, K, seed, alpha=1.0, sub=False, exp=False, div=False, want_c=True,
-        want_max=True, want_sum=True):
+        want_max=True, want_sum=True, variant=None):
     A, Bt = operands(M, N, K, seed)
     rng = np.random.default_rng(seed)
     row_sub = rng.standard_normal(M).astype(np.float32) if sub else None
@@ -39,7 +39,7 @@ def run(ctx, oracle, M, N, K, seed, alpha=1.0, sub=False, exp=False, div=False, 
     ctx.gemm_bf16_epilogue(A, Bt, C, alpha=alpha,
                            row_sub=torch.from_numpy(row_sub).cuda() if sub else None, apply_exp=exp,
                            row_div=torch.from_numpy(row_div).cuda() if div else None,
-                           row_max=rmax, row_sum=rsum)
+                           row_max=rmax, row_sum=rsum, variant=variant)
     ctx.sync()
     oracle.set_threads(oracle.max_threads())
     t, tmax, tsum = oracle.gemm_bf16_epilogue(bits(A), bits(Bt), alpha, row_sub, exp, row_div)
@@ -66,6 +66,18 @@ def test_exp_matrix_consumer(ctx, oracle, shape):
 @pytest.mark.parametrize("shape", [(256, 512, 128), (513, 300, 64)])
 def test_subtract_exp_divide_chain(ctx, oracle, shape):
     run(ctx, oracle, *shape, seed=2 + sum(shape), alpha=0.5, sub=True, exp=True, div=True)
+
+
+@pytest.mark.parametrize("variant", [1, 2])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (300, 700, 192), (1, 8, 8), (129, 257, 72), (1024, 1280, 512)])
+def test_both_kernels_with_every_consumer(ctx, oracle, shape, variant):
+    """Single-CTA tiles (1) and CTA pairs (2), forced; large outputs take the pair kernel by default."""
+    run(ctx, oracle, *shape, seed=7 + sum(shape), alpha=0.5, sub=True, exp=True, div=True, variant=variant)
+    run(ctx, oracle, *shape, seed=8 + sum(shape), want_c=False, variant=variant)
+
+
+def test_large_output_takes_the_pair_kernel(ctx, oracle):
+    run(ctx, oracle, 2560, 2560, 256, seed=11, exp=True)      # 100 tiles of 256 x 256 >= 74 pairs
 
 
 def test_negative_values_take_the_right_maximum(ctx, oracle):
