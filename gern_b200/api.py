@@ -45,6 +45,8 @@ SIGNATURES = {
                              ctypes.c_float, _vp],
     "gb200_attention_bf16_cluster": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                      ctypes.c_float, _int, _vp],
+    "gb200_attention_bf16_splitkv": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
+                                     ctypes.c_float, _vp, _int],
     "gb200_attention_bf16_variant": [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64,
                                      ctypes.c_float, _vp, _int],
     "gb200_gemm_f32_host": [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int],
@@ -313,9 +315,15 @@ class Context:
         _check(lib.gb200_blur3x3_f32_band(self.handle, _ptr(x), _ld(x), rows, cols, hp, hl, _ptr(out),
                                           _ld(out), _stream(stream)), "gb200_blur3x3_f32_band")
 
-    def attention_bf16(self, Q, K, V, O, scale, stream=None, variant=None):
+    def attention_bf16(self, Q, K, V, O, scale, stream=None, variant=None, splits=None):
         nq, d = Q.shape
         nkv = K.shape[0]
+        if splits is not None:
+            _check(lib.gb200_attention_bf16_splitkv(self.handle, _ptr(Q), _ld(Q), _ptr(K), _ld(K), _ptr(V),
+                                                    _ld(V), _ptr(O), _ld(O), nq, nkv, d,
+                                                    ctypes.c_float(scale), _stream(stream), int(splits)),
+                   "gb200_attention_bf16_splitkv")
+            return
         if variant is not None:
             _check(lib.gb200_attention_bf16_variant(self.handle, _ptr(Q), _ld(Q), _ptr(K), _ld(K), _ptr(V),
                                                     _ld(V), _ptr(O), _ld(O), nq, nkv, d,

@@ -122,11 +122,17 @@ __device__ __forceinline__ uint64_t mufu_exp2_pair(uint64_t x2) {
     return pk2(fast_exp2(x0), fast_exp2(x1));
 }
 
+// SPLIT = false: a CTA walks all K/V blocks of its two Q tiles and stores bf16 O.
+// SPLIT = true:  blockIdx.y picks a range of `blocks_per_split` K/V blocks; the CTA stores its
+// unnormalised fp32 O, its reference maximum and its row sum as a partial result, and
+// attention_combine_kernel merges the ranges.  Used when there are too few Q tiles to fill the GPU.
+template <bool SPLIT>
 __global__ void __launch_bounds__(attn::NUM_THREADS, 1)
 attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, __nv_bfloat16 *__restrict__ O,
-                      int64_t ldo, int nq, int nkv, float scale_log2, int *status) {
+                      int64_t ldo, int nq, int nkv, float scale_log2, int *status,
+                      int blocks_per_split, float *__restrict__ part_o, float *__restrict__ part_ml) {
     using namespace attn;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -145,7 +151,10 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q0 = blockIdx.x * (BM * TILES);
-    const int n_blocks = (nkv + BN - 1) / BN;
+    // K/V blocks [b0, b0 + n_blocks) are this CTA's; j below counts from b0
+    const int total_blocks = (nkv + BN - 1) / BN;
+    const int b0 = SPLIT ? static_cast<int>(blockIdx.y) * blocks_per_split : 0;
+    const int n_blocks = SPLIT ? max(0, min(blocks_per_split, total_blocks - b0)) : total_blocks;
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_q);
@@ -193,8 +202,8 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const CUtensorMap *tm = (u & 1) ? &tmap_v : &tmap_k;
                 unsigned char *dst = sKV + slot * TILE_BYTES;
                 mbar_expect_tx(&kv_full[slot], TILE_BYTES);
-                tma_load_2d(dst, tm, 0, (u >> 1) * BN, &kv_full[slot]);
-                tma_load_2d(dst + CHUNK_BYTES, tm, 64, (u >> 1) * BN, &kv_full[slot]);
+                tma_load_2d(dst, tm, 0, (b0 + (u >> 1)) * BN, &kv_full[slot]);
+                tma_load_2d(dst + CHUNK_BYTES, tm, 64, (b0 + (u >> 1)) * BN, &kv_full[slot]);
             }
         }
     } else if (warp == 8) {
@@ -282,7 +291,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             if (!mbar_wait(&s_full[t], j & 1, status, 308)) { ok = false; break; }
             if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 0, j);
             tc_fence_after();
-            const int valid = min(BN, nkv - j * BN);
+            const int valid = min(BN, nkv - (b0 + j) * BN);
 
             // pass 1: row maximum of the block.  All four TMEM loads are in flight at once (a TMEM
             // round trip costs a few hundred cycles); the 128 values are dropped again so that the
@@ -408,8 +417,30 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (ok && n_blocks > 0) ok = mbar_wait(&o_full[t], 0, status, 310);
         if (ok && n_blocks > 0) {
             tc_fence_after();
-            const float inv = 1.0f / l;
             const int row = q0 + t * BM + row_in_tile;
+            if (SPLIT) {
+                // partial result of this K/V range: O as accumulated (relative to m_used), m_used, l
+                if (row < nq) {
+                    const int64_t slot = static_cast<int64_t>(blockIdx.y) * nq + row;
+                    part_ml[2 * slot] = m_used;
+                    part_ml[2 * slot + 1] = l;
+                }
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(t_o + c * 32, o);
+                    tmem_ld_wait();
+                    if (row < nq) {
+                        float4 *dst = reinterpret_cast<float4 *>(
+                            part_o + (static_cast<int64_t>(blockIdx.y) * nq + row) * D + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q)
+                            dst[q] = make_float4(__uint_as_float(o[4 * q]), __uint_as_float(o[4 * q + 1]),
+                                                 __uint_as_float(o[4 * q + 2]), __uint_as_float(o[4 * q + 3]));
+                    }
+                }
+            } else {
+            const float inv = 1.0f / l;
             const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(O) & 15) == 0);
             const bool vec32_ok = (ldo % 16 == 0) && ((reinterpret_cast<uintptr_t>(O) & 31) == 0);
 #pragma unroll 1
@@ -446,6 +477,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     }
                 }
             }
+            }
         }
     }
 
@@ -454,6 +486,50 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, attn::TMEM_COLS);
+    }
+}
+
+// Merges the partial results of `splits` K/V ranges: with M = max_s m_s,
+// O = sum_s 2^(m_s - M) O_s / sum_s 2^(m_s - M) l_s.  One warp per row, four columns per lane.
+__global__ void __launch_bounds__(256)
+attention_combine_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
+                         __nv_bfloat16 *__restrict__ O, int64_t ldo, int nq, int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= nq) return;
+    float m_all = -FLT_MAX;
+    for (int s = 0; s < splits; ++s) {
+        const float2 ml = *reinterpret_cast<const float2 *>(part_ml + 2 * (static_cast<int64_t>(s) * nq + row));
+        if (ml.y > 0.0f) m_all = fmaxf(m_all, ml.x);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l_all = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+        const int64_t slot = static_cast<int64_t>(s) * nq + row;
+        const float2 ml = *reinterpret_cast<const float2 *>(part_ml + 2 * slot);
+        if (!(ml.y > 0.0f)) continue;      // a range that saw no block contributes nothing
+        const float w = exp2f(ml.x - m_all);
+        const float4 o = *reinterpret_cast<const float4 *>(part_o + slot * attn::D + lane * 4);
+        acc.x = fmaf(w, o.x, acc.x);
+        acc.y = fmaf(w, o.y, acc.y);
+        acc.z = fmaf(w, o.z, acc.z);
+        acc.w = fmaf(w, o.w, acc.w);
+        l_all = fmaf(w, ml.y, l_all);
+    }
+    const float inv = 1.0f / l_all;
+    __nv_bfloat16 *dst = O + static_cast<int64_t>(row) * ldo + lane * 4;
+    if ((ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(O) & 7) == 0)) {
+        uint2 v;
+        v.x = pack_bf16(acc.x * inv, acc.y * inv);
+        v.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2 *>(dst) = v;
+    } else {
+        dst[0] = __float2bfloat16_rn(acc.x * inv);
+        dst[1] = __float2bfloat16_rn(acc.y * inv);
+        dst[2] = __float2bfloat16_rn(acc.z * inv);
+        dst[3] = __float2bfloat16_rn(acc.w * inv);
     }
 }
 
@@ -468,9 +544,11 @@ int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void
 
 // kernel_choice: 0 = pick, 1 = one CTA per two Q tiles, 2 = CTA pairs with two Q tiles per CTA
 // (attention_pair.cu).
+// kv_splits: 0 = pick (split the K/V range when the Q tiles alone leave more than half of the SMs
+// idle), 1 = never split, n > 1 = that many ranges (fewer if there are not enough K/V blocks).
 int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                        const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
-                       int64_t d, float scale, cudaStream_t stream, int kernel_choice = 0) {
+                       int64_t d, float scale, cudaStream_t stream, int kernel_choice = 0, int kv_splits = 0) {
     using namespace attn;
     GB200_REQUIRE(d == D, GB200_ERR_UNSUPPORTED, "attention: d must be %d in this build (got %lld)",
                   D, (long long)d);
@@ -487,14 +565,46 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     rc = get_tmap_2d(ctx, V, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)d, (uint64_t)nkv,
                      (uint64_t)ldv * 2, 64, BN, CU_TENSOR_MAP_SWIZZLE_128B, &tv);
     if (rc) return rc;
-    rc = ensure_dynamic_smem(ctx, attention_bf16_kernel, SMEM_BYTES);
-    if (rc) return rc;
     const float scale_log2 = scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)((nq + BM * TILES - 1) / (BM * TILES));
-    GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES, stream,
-                              tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv,
-                              scale_log2, ctx->d_status));
-    return after_launch(ctx, "attention_bf16_kernel");
+    const int total_blocks = (int)((nkv + BN - 1) / BN);
+    int splits = kv_splits;
+    if (splits == 0) {
+        // One CTA per two Q tiles fills the GPU from 74 CTAs up.  Below that, K/V ranges of at
+        // least two blocks go to the idle SMs; the combine pass costs one read of the partials.
+        splits = 1;
+        if ((int)grid * 2 <= ctx->sm_count && total_blocks >= 4) {
+            splits = ctx->sm_count / (int)grid;
+            if (splits > total_blocks / 2) splits = total_blocks / 2;
+        }
+    }
+    if (splits > total_blocks) splits = total_blocks;
+    if (splits <= 1) {
+        rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<false>, SMEM_BYTES);
+        if (rc) return rc;
+        GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<false>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+                                  stream, tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv,
+                                  scale_log2, ctx->d_status, 0, static_cast<float *>(nullptr),
+                                  static_cast<float *>(nullptr)));
+        return after_launch(ctx, "attention_bf16_kernel");
+    }
+    const int per = (total_blocks + splits - 1) / splits;
+    splits = (total_blocks + per - 1) / per;          // every range holds at least one block
+    rc = workspace_reserve(ctx, (size_t)splits * (size_t)nq * (D + 2) * sizeof(float));
+    if (rc) return rc;
+    float *part_o = static_cast<float *>(ctx->workspace);
+    float *part_ml = part_o + (size_t)splits * (size_t)nq * D;
+    rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<true>, SMEM_BYTES);
+    if (rc) return rc;
+    GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<true>, dim3(grid, (unsigned)splits), dim3(NUM_THREADS),
+                              (size_t)SMEM_BYTES, stream, tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo,
+                              (int)nq, (int)nkv, scale_log2, ctx->d_status, per, part_o, part_ml));
+    rc = after_launch(ctx, "attention_bf16_kernel<split>");
+    if (rc) return rc;
+    GB200_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3((unsigned)((nq + 7) / 8)), dim3(256), 0, stream,
+                              static_cast<const float *>(part_o), static_cast<const float *>(part_ml),
+                              static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, splits));
+    return after_launch(ctx, "attention_combine_kernel");
 }
 
 static int check_attention_args(const void *Q, int64_t ldq, const void *K, int64_t ldk,
@@ -514,7 +624,7 @@ static int check_attention_args(const void *Q, int64_t ldq, const void *K, int64
     return GB200_OK;
 }
 
-int kernel_regs_attention() { return kernel_registers(attention_bf16_kernel); }
+int kernel_regs_attention() { return kernel_registers(attention_bf16_kernel<false>); }
 
 }  // namespace gb200
 
@@ -566,6 +676,21 @@ int gb200_attention_bf16_variant(gb200_ctx *ctx, const void *Q, int64_t ldq, con
     if (rc) return rc < 0 ? rc : GB200_OK;
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
                               static_cast<cudaStream_t>(stream), variant);
+}
+
+// Test / benchmark hook: the single-CTA kernel with the number of K/V ranges chosen by the caller
+// (1 = no split, 0 = let the library pick).
+int gb200_attention_bf16_splitkv(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
+                                 const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
+                                 int64_t nkv, int64_t d, float scale, void *stream, int splits) {
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(splits >= 0 && splits <= 1024, GB200_ERR_INVALID_ARG, "splits out of range");
+    rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
+    if (rc) return rc < 0 ? rc : GB200_OK;
+    return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,
+                              static_cast<cudaStream_t>(stream), 1, splits);
 }
 
 int gb200_attention_bf16_host(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K,

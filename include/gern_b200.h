@@ -199,7 +199,9 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
  * all row-major; S and P stay in TMEM / shared memory.  d must be 128 in this build.  The
  * nearest reference analogue is the chained-GEMM fusion with a per-tile temporary
  * (test/test-cpu-mm.cpp:266-408).  `scale` must be positive and finite (the row maximum is taken
- * before scaling); anything else is refused with GB200_ERR_INVALID_ARG. */
+ * before scaling); anything else is refused with GB200_ERR_INVALID_ARG.  When nq is too small to
+ * give every SM a pair of Q tiles, the K/V range is cut across thread blocks and a second kernel
+ * merges the partial results (kept in the context's workspace). */
 int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                          int64_t nkv, int64_t d, float scale, void *stream);

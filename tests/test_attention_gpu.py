@@ -129,9 +129,10 @@ def test_full_size_sampled(ctx, oracle):
     # and row by row, so that one bad row cannot hide in the norm of 640
     err = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
     assert err.max() <= 2e-2, (idx[int(err.argmax())], float(err.max()))
-    # rows are independent: any row block alone gives the same bits
+    # rows are independent: any row block alone gives the same bits (with the K/V range left whole,
+    # as in the full-size run; a small problem would otherwise have its range split across CTAs)
     o2 = torch.zeros((256, 128), dtype=torch.bfloat16, device="cuda")
-    ctx.attention_bf16(q[1024:1280].contiguous(), k, v, o2, scale)
+    ctx.attention_bf16(q[1024:1280].contiguous(), k, v, o2, scale, splits=1)
     ctx.sync()
     assert torch.equal(o2, o[1024:1280])
 
@@ -160,3 +161,50 @@ def test_non_positive_or_non_finite_scale_is_refused(ctx, scale):
         assert e.value.code == -1 and "scale must be positive" in str(e.value)
     ctx.sync()
     assert bool((o == 5.0).all())
+
+
+@pytest.mark.parametrize("nq,nkv,splits", [(256, 1024, 1), (256, 1024, 2), (256, 1024, 8), (100, 1000, 3), (640, 4096, 16),
+                                           (130, 300, 5), (1, 129, 2), (512, 2048, 0), (300, 700, 64)])
+def test_kv_ranges_split_across_ctas(ctx, oracle, nq, nkv, splits):
+    """Few Q tiles: the K/V range is cut across CTAs (each keeps its unnormalised O, reference
+    maximum and row sum) and a combine pass merges the ranges.  splits = 1 forces the unsplit
+    kernel, 0 lets the library choose, more splits than blocks are clamped."""
+    q, k, v = make(nq, nkv, nq * 3 + nkv + splits)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / np.sqrt(128.0)
+    ctx.attention_bf16(q, k, v, o, scale, splits=splits)
+    ctx.sync()
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), scale)
+    oracle.set_threads(1)
+    got = o.float().cpu().numpy()
+    assert frob(got, want) <= 1e-2
+    # the unsplit kernel on the same input: the combine adds only fp32 reassociation and one bf16 rounding
+    o1 = torch.zeros_like(o)
+    ctx.attention_bf16(q, k, v, o1, scale, splits=1)
+    ctx.sync()
+    assert frob(got, o1.float().cpu().numpy().astype(np.float64)) <= 4e-3
+
+
+def test_split_ranges_with_growing_maxima(ctx, oracle):
+    """Ranges whose reference maxima differ widely: the combine's 2^(m_s - M) weights must hold."""
+    nq, nkv = 256, 2048
+    q, k, v = make(nq, nkv, 9)
+    ramp = torch.linspace(0.2, 3.0, nkv, device="cuda").unsqueeze(1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    ctx.attention_bf16(q, k, v, o, 1.0, splits=8)
+    ctx.sync()
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), 1.0)
+    assert frob(o.float().cpu().numpy(), want) <= 1e-2
+
+
+def test_split_output_with_a_padded_pitch(ctx, oracle):
+    nq, nkv = 200, 1536
+    q, k, v = make(nq, nkv, 21)
+    o = torch.full((nq, 130), 3.0, dtype=torch.bfloat16, device="cuda")     # rows not 8-byte aligned
+    ctx.attention_bf16(q, k, v, o[:, :128], 0.1, splits=4)
+    ctx.sync()
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), 0.1)
+    assert frob(o[:, :128].float().cpu().numpy(), want) <= 1e-2
+    assert bool((o[:, 128:] == 3.0).all())
