@@ -201,14 +201,30 @@ int gemm_f32_tc_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const floa
 #define GB200_GEMM_F32_TC_MIN_FLOP 6.0e8   // measured: 512^3 19.0 vs 24.8 us, 768^3 43.6 vs 34.7 us
 #endif
 
-// kernel_choice: 0 = pick, 1 = CUDA cores, 2 = tensor cores (three-way bf16 split).
+int gemm_f32_fused_launch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,
+                          int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate, cudaStream_t stream);
+
+// The single-launch tensor-core kernel (gemm_f32_fused.cu) is selectable but never picked: from cold
+// L2 it measured 22 / 33 / 45 / 57 us at 256^3 / 512^3 / 768^3 / 1024^3 against 11 / 21 / 47 / 110 us
+// for the CUDA-core kernels and 22 / 30 / 40 / 47 us for the three-launch tensor-core path, so one of
+// the other two is faster at every size (its eight converting warps are bound by the fp32 -> bf16
+// conversions, three per operand element, not by the MMAs).
+#ifndef GB200_GEMM_F32_FUSED_MIN_FLOP
+#define GB200_GEMM_F32_FUSED_MIN_FLOP 1.0e30
+#endif
+
+// kernel_choice: 0 = pick, 1 = CUDA cores, 2 = tensor cores with split pre-passes (three launches),
+// 3 = tensor cores with the split inside the kernel (one launch).
 int gemm_f32_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
                       float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
                       cudaStream_t stream, int kernel_choice = 0) {
     const bool tc_ok = ctx->encode_tiled != nullptr && K > 0;
-    const bool tc_pays = 2.0 * (double)M * (double)N * (double)K >= GB200_GEMM_F32_TC_MIN_FLOP;
+    const double flop = 2.0 * (double)M * (double)N * (double)K;
+    const bool tc_pays = flop >= GB200_GEMM_F32_TC_MIN_FLOP;
     if (tc_ok && (kernel_choice == 2 || (kernel_choice == 0 && tc_pays)))
         return gemm_f32_tc_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream);
+    if (K > 0 && (kernel_choice == 3 || (kernel_choice == 0 && flop >= GB200_GEMM_F32_FUSED_MIN_FLOP)))
+        return gemm_f32_fused_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream);
     const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
     const bool big = big_tiles >= 2 * (int64_t)ctx->sm_count;
     const int bm = big ? 128 : 32;
