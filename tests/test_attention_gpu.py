@@ -208,3 +208,25 @@ def test_split_output_with_a_padded_pitch(ctx, oracle):
     want = oracle.attention_bf16(bits(q), bits(k), bits(v), 0.1)
     assert frob(o[:, :128].float().cpu().numpy(), want) <= 1e-2
     assert bool((o[:, 128:] == 3.0).all())
+
+
+def test_cluster_entry_point(ctx, oracle):
+    """gb200_attention_bf16_cluster: clusters of one and of two thread blocks give the same bits
+    (with the K/V range left whole); other sizes are refused."""
+    from gern_b200 import api
+    import ctypes
+    nq, nkv = 1100, 256            # few K/V blocks: no range splitting in either kernel
+    q, k, v = make(nq, nkv, 77)
+    outs = []
+    for cluster_x in (1, 2):
+        o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+        rc = api.lib.gb200_attention_bf16_cluster(ctx.handle, q.data_ptr(), 128, k.data_ptr(), 128, v.data_ptr(), 128,
+                                                  o.data_ptr(), 128, nq, nkv, 128, ctypes.c_float(0.09), cluster_x, None)
+        assert rc == 0
+        ctx.sync()
+        outs.append(o)
+    assert torch.equal(outs[0], outs[1])
+    want = oracle.attention_bf16(bits(q), bits(k), bits(v), 0.09)
+    assert frob(outs[0].float().cpu().numpy(), want) <= 1e-2
+    assert api.lib.gb200_attention_bf16_cluster(ctx.handle, q.data_ptr(), 128, k.data_ptr(), 128, v.data_ptr(), 128,
+                                                outs[0].data_ptr(), 128, nq, nkv, 128, ctypes.c_float(0.09), 3, None) == -3

@@ -58,3 +58,21 @@ def test_product_does_not_touch_the_oracle():
                 if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp")):
                     src = open(os.path.join(dirpath, f), errors="replace").read()
                     assert "oracle" not in src.lower(), f"{f} names the oracle"
+
+
+def test_kernel_resources_come_from_the_planned_layouts():
+    """gb200_kernel_resources_query answers without a device (registers are then -1): dynamic shared
+    memory within an sm_100a block's 227 KB, the pair kernels in clusters of two, 512 TMEM columns."""
+    from gern_b200 import api
+    seen = {}
+    for name in ("gemm_bf16_tc", "gemm_bf16_2cta", "attention_bf16", "attention_bf16_pair"):
+        r = api.kernel_resources(name)
+        assert 64 * 1024 < r.dynamic_smem_bytes <= 227 * 1024, name
+        assert r.dynamic_smem_bytes % 128 == 0 and r.tmem_columns == 512 and r.threads % 32 == 0
+        assert r.cluster_x == (2 if name in ("gemm_bf16_2cta", "attention_bf16_pair") else 1)
+        seen[name] = r.dynamic_smem_bytes
+    # four stages of (128 + 256) x 64 bf16 and six stages of 2 x 128 x 64 bf16, plus barriers and slack
+    assert seen["gemm_bf16_tc"] >= 4 * 49152 + 1024 and seen["gemm_bf16_2cta"] >= 6 * 32768 + 1024
+    with pytest.raises(api.GernB200Error) as e:
+        api.kernel_resources("no_such_kernel")
+    assert e.value.code == -1

@@ -306,3 +306,22 @@ def test_host_entry_points(ctx, oracle):
     cb = np.zeros((256, 512), np.uint16)
     ctx.gemm_bf16_host(ab, bb, cb)
     assert frob(pyoracle.bf16_bits_to_f32(cb), oracle.gemm_bf16(ab, bb)) <= 3e-3
+
+
+@pytest.mark.parametrize("cluster_x", [1, 2])
+def test_bf16_cluster_entry_point(ctx, oracle, cluster_x):
+    """gb200_gemm_bf16_cluster: 1 = single-CTA tiles, 2 = CTA pairs; other sizes are refused."""
+    from gern_b200 import api
+    m, n, k = 300, 520, 200
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = (torch.randn((m, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    c = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    rc = api.lib.gb200_gemm_bf16_cluster(ctx.handle, a.data_ptr(), k, b.data_ptr(), k, c.data_ptr(), n, m, n, k,
+                                         cluster_x, None)
+    assert rc == 0
+    ctx.sync()
+    want = oracle.gemm_bf16(np.ascontiguousarray(bits(a)), np.ascontiguousarray(bits(b)))
+    assert frob(c.float().cpu().numpy(), want) <= 3e-3
+    assert api.lib.gb200_gemm_bf16_cluster(ctx.handle, a.data_ptr(), k, b.data_ptr(), k, c.data_ptr(), n, m, n, k,
+                                           4, None) == -3
