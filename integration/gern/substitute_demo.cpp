@@ -4,6 +4,10 @@
 //
 //   gern_b200_substitute --repo <root of this repository> {blur|mm_cpu|softmax|unmatched}
 //
+// Built a second time with -DDEMO_PATCHED_RUNNER against a Runner that carries
+// runner_substitute.patch (gern_b200_patched): the demo then hands the ORIGINAL program to
+// Runner::compile with nothing but a file name, and the substitution happens inside Gern.
+//
 // Prints `matched: <kernel>` and, after Runner::compile, `compiled: <file>`; then calls evaluate on
 // small host matrices.  Exit status as in run_program.cpp (4 = evaluate failed; without a GPU that
 // is the library's "no CUDA device").  `unmatched` shows a program that is left alone.
@@ -70,6 +74,14 @@ int main(int argc, char **argv) {
             Variable ti("ti"), tj("tj"), tk("tk"), k_dim("k_dim");
             program = {(Tile(C_DS["row"], ti))(Tile(C_DS["col"], tj)((Reduce(k_dim, tk))(matrix_multiply(A_DS, B_DS, C_DS, k_dim))))};
             args = {{"A", &sq_a}, {"B", &sq_b}, {"C", &sq_c}, {"k_dim", &k_dim_val}};
+#ifdef DEMO_PATCHED_RUNNER
+            // a caller written for the original schedule also passes its tile sizes: the patched
+            // Runner::evaluate accepts and ignores them
+            static int64_t tile = 16;
+            args["ti"] = &tile;
+            args["tj"] = &tile;
+            args["tk"] = &tile;
+#endif
         } else if (what == "softmax") {
             // the five row-softmax pieces of apps/common/annot/functions.h:9-173 under one row tile
             using MatAnnot = ::annot::MatrixGPUSequential<R, C, 1>;
@@ -107,13 +119,22 @@ int main(int argc, char **argv) {
     for (const auto &n : sub.arguments) std::printf(" %s", n.c_str());
     std::printf("\n");
 
-    Runner run(sub.program);
     Runner::Options o;
-    o.filename = "gern_b200_substituted_" + what + ".cpp";
     o.prefix = "/tmp";
+#ifdef DEMO_PATCHED_RUNNER
+    // the patched Runner substitutes by itself and adds the include and link flags of the library
+    setenv("GERN_B200_OPERANDS", "host", 1);
+    Runner run(program);
+    o.filename = "gern_b200_patched_" + what + ".cpp";
+    o.include = " -O2 ";
+    (void)cuda;
+#else
+    Runner run(sub.program);
+    o.filename = "gern_b200_substituted_" + what + ".cpp";
     o.cpp_std = "c++17";
     o.include = " -O2 -I " + repo + "/integration/gern -I " + repo + "/include -I " + cuda + "/include";
     o.ldflags = "-L " + repo + "/gern_b200 -lgern_b200 -Wl,-rpath," + repo + "/gern_b200 -L " + cuda + "/lib64 -lcudart";
+#endif
     try {
         run.compile(o);
     } catch (const std::exception &e) {

@@ -144,31 +144,40 @@ def test_bf16_matmul_softmax_and_chain_through_gern(tmp_path, oracle, golden, go
 
 
 # ---------------------------------------------------------------------------------------------
-# Pattern substitution: programs written against the reference's OWN annotation headers
-SUBSTITUTE = os.path.join(ROOT, "integration", "_ref", "gern_b200_substitute")
-needs_substitute = pytest.mark.skipif(not os.path.exists(SUBSTITUTE),
-                                      reason="integration/_ref/gern_b200_substitute not built (needs the Gern tree at build time)")
+# Pattern substitution: programs written against the reference's OWN annotation headers.
+# `substitute`: the program is rewritten by gern::b200::substitute() and handed to the unmodified
+# Runner.  `patched`: the ORIGINAL program is handed to a Runner built from the reference's
+# runner.cpp plus integration/gern/runner_substitute.patch, which rewrites it inside
+# Runner::compile and adds the library's include and link flags itself.
+DEMOS = {"substitute": (os.path.join(ROOT, "integration", "_ref", "gern_b200_substitute"), "gern_b200_substituted_"),
+         "patched": (os.path.join(ROOT, "integration", "_ref", "gern_b200_patched"), "gern_b200_patched_")}
 SUBSTITUTED = {"blur": ("blur3x3", "gb200_host::blur3x3(input, output)"),
                "mm_cpu": ("matrix_multiply", "gb200_host::matrix_multiply(A, B, C, k_dim)"),
                "softmax": ("softmax_rows", "gb200_host::softmax_rows(input, output)")}
 
 
-def run_substitute(what, cwd):
-    return subprocess.run([SUBSTITUTE, "--repo", ROOT, what], capture_output=True, text=True, cwd=cwd, timeout=600)
+def run_demo(how, what, cwd):
+    binary = DEMOS[how][0]
+    if not os.path.exists(binary):
+        pytest.skip(f"{os.path.relpath(binary, ROOT)} not built (needs the Gern tree at build time)")
+    return subprocess.run([binary, "--repo", ROOT, what], capture_output=True, text=True, cwd=cwd, timeout=600)
 
 
-@needs_substitute
+@pytest.mark.parametrize("how", sorted(DEMOS))
 @pytest.mark.parametrize("what", sorted(SUBSTITUTED))
-def test_reference_programs_are_rewritten_onto_the_library(tmp_path, what):
+def test_reference_programs_are_rewritten_onto_the_library(tmp_path, what, how):
     """The blur program of apps/blur/blur.cpp:46-73, the tiled matmul of test/test-cpu-mm.cpp:13-83 and
     the five softmax pieces of apps/common/annot/functions.h, built with the reference's own
-    annotation classes, are recognised by gern::b200::substitute(); the rewritten program goes
-    through the unmodified Runner, and its hook is one call into the library."""
+    annotation classes, are recognised by gern::b200::substitute() -- called by the demo, or by the
+    patched Runner::compile (src/codegen/runner.cpp:11) -- and the generated hook is one call into
+    the library.  The patched Runner::evaluate also takes the tile sizes the original schedule's
+    caller passes (the matmul demo passes ti, tj, tk) and ignores them."""
     kernel, call = SUBSTITUTED[what]
-    res = run_substitute(what, tmp_path)
+    res = run_demo(how, what, tmp_path)
+    generated = f"/tmp/{DEMOS[how][1]}{what}.cpp"
     assert f"matched: {kernel}" in res.stdout, res.stdout + res.stderr
-    assert f"compiled: /tmp/gern_b200_substituted_{what}.cpp" in res.stdout, res.stderr
-    src = open(f"/tmp/gern_b200_substituted_{what}.cpp").read()
+    assert f"compiled: {generated}" in res.stdout, res.stderr
+    src = open(generated).read()
     assert call in src and "for(" not in src        # one library call, the schedule's loops are gone
     if have_gpu():
         assert res.returncode == 0 and "evaluated: result as expected" in res.stdout, res.stderr
@@ -176,15 +185,39 @@ def test_reference_programs_are_rewritten_onto_the_library(tmp_path, what):
         assert res.returncode == 4 and "status -4" in res.stderr and "no CUDA device" in res.stderr
 
 
-@needs_substitute
-def test_programs_without_a_fused_kernel_are_left_alone(tmp_path):
-    res = run_substitute("unmatched", tmp_path)      # blur with stride 5
+@pytest.mark.parametrize("how", sorted(DEMOS))
+def test_programs_without_a_fused_kernel_are_left_alone(tmp_path, how):
+    res = run_demo(how, "unmatched", tmp_path)      # blur with stride 5
     assert res.returncode == 0 and "matched: none" in res.stdout
 
 
-@needs_substitute
+def test_the_runner_patch_applies_to_the_reference_source(tmp_path):
+    """runner_substitute.patch is a unified diff of src/codegen/runner.cpp; it has to apply cleanly
+    to the tree the oracle was built from, and everything it adds sits under GERN_B200_ROOT."""
+    from oracle import pyoracle
+    ref = pyoracle.find_reference()
+    if ref is None:
+        pytest.skip("no Gern tree here")
+    import shutil
+    os.makedirs(tmp_path / "src" / "codegen")
+    shutil.copy(os.path.join(ref, "src", "codegen", "runner.cpp"), tmp_path / "src" / "codegen" / "runner.cpp")
+    patch = os.path.join(ROOT, "integration", "gern", "runner_substitute.patch")
+    res = subprocess.run(["patch", "-p1", "--dry-run", "-i", patch], cwd=tmp_path, capture_output=True, text=True)
+    assert res.returncode == 0, res.stdout + res.stderr
+    added = [l[1:] for l in open(patch) if l.startswith("+") and not l.startswith("+++")]
+    depth = 0
+    for line in added:
+        if line.startswith("#ifdef GERN_B200_ROOT"):
+            depth += 1
+        elif line.startswith("#endif"):
+            depth -= 1
+        else:
+            assert depth == 1 or not line.strip(), line
+
+
 @gpu
+@pytest.mark.parametrize("how", sorted(DEMOS))
 @pytest.mark.parametrize("what", sorted(SUBSTITUTED))
-def test_substituted_programs_evaluate_on_the_gpu(tmp_path, what):
-    res = run_substitute(what, tmp_path)
+def test_substituted_programs_evaluate_on_the_gpu(tmp_path, what, how):
+    res = run_demo(how, what, tmp_path)
     assert res.returncode == 0 and "evaluated: result as expected" in res.stdout, res.stdout + res.stderr
