@@ -316,6 +316,9 @@ class Context:
                                           _ld(out), _stream(stream)), "gb200_blur3x3_f32_band")
 
     def attention_bf16(self, Q, K, V, O, scale, stream=None, variant=None, splits=None):
+        """splits (test hook): 0 = the library's choice, 1 = whole Q tile pairs per thread block,
+        n > 1 = that many K/V ranges and a combine pass, -1 = equal runs of (pair, K/V block) units
+        per thread block, merged inside the kernel."""
         nq, d = Q.shape
         nkv = K.shape[0]
         if splits is not None:

@@ -63,11 +63,15 @@ constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 #endif
 
 #ifdef GB200_ATTN_TRACE
-// Debug-only timeline (compiled out of the library): CTA 0 records clock64() at a few points.
-__device__ long long g_attn_trace[16 * 64];
+#ifndef GB200_ATTN_TRACE_CTA
+#define GB200_ATTN_TRACE_CTA 0
+#endif
+// Debug-only timeline (compiled out of the library): one CTA records clock64() at a few points,
+// indexed by the K/V blocks it has done so far.
+__device__ long long g_attn_trace[28 * 64];
 #define ATTN_TRACE(slot, j)                                                          \
     do {                                                                             \
-        if (blockIdx.x == 0 && (j) < 64) g_attn_trace[(slot) * 64 + (j)] = clock64(); \
+        if (blockIdx.x == GB200_ATTN_TRACE_CTA && (j) < 64) g_attn_trace[(slot) * 64 + (j)] = clock64(); \
     } while (0)
 #else
 #define ATTN_TRACE(slot, j) do { } while (0)
@@ -122,17 +126,107 @@ __device__ __forceinline__ uint64_t mufu_exp2_pair(uint64_t x2) {
     return pk2(fast_exp2(x0), fast_exp2(x1));
 }
 
-// SPLIT = false: a CTA walks all K/V blocks of its two Q tiles and stores bf16 O.
-// SPLIT = true:  blockIdx.y picks a range of `blocks_per_split` K/V blocks; the CTA stores its
-// unnormalised fp32 O, its reference maximum and its row sum as a partial result, and
-// attention_combine_kernel merges the ranges.  Used when there are too few Q tiles to fill the GPU.
-template <bool SPLIT>
+// The bf16 output and how one thread stores 32 columns of one row of it.
+struct OutRows {
+    __nv_bfloat16 *O;
+    int64_t ldo;
+    int nq;
+    // 32 fp32 values of row `row`, columns [32c, 32c + 32), times inv -> bf16 -> global
+    __device__ __forceinline__ void store_chunk(int row, int c, const uint32_t (&o)[32], float inv) const {
+        if (row >= nq) return;
+        const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(O) & 15) == 0);
+        const bool vec32_ok = (ldo % 16 == 0) && ((reinterpret_cast<uintptr_t>(O) & 31) == 0);
+        __nv_bfloat16 *dst = O + static_cast<int64_t>(row) * ldo + c * 32;
+        if (vec32_ok) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    w[i] = pack_bf16(__uint_as_float(o[16 * h + 2 * i]) * inv,
+                                     __uint_as_float(o[16 * h + 2 * i + 1]) * inv);
+                st_global_256(dst + 16 * h, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
+            }
+        } else if (vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
+                v.y = pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
+                v.z = pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
+                v.w = pack_bf16(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
+                *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(o[i]) * inv);
+        }
+    }
+};
+
+// What one CTA works on is a list of segments: a pair of Q tiles (256 rows) and a range of K/V
+// blocks.  The three schedules differ only in that list.
+enum : int {
+    WHOLE = 0,     // blockIdx.x = pair; all K/V blocks; bf16 O stored directly
+    SPLIT = 1,     // blockIdx.x = pair, blockIdx.y = range of `per` K/V blocks; the CTA stores its
+                   // unnormalised fp32 O, reference maximum and row sum, attention_combine_kernel
+                   // merges the ranges.  Used when there are too few Q tiles to fill the GPU.
+    BALANCED = 2,  // the pairs x blocks units, pair-major, are cut into equal runs of `per` units,
+                   // one run per CTA (so a CTA may finish one pair and start the next).  A pair
+                   // that several CTAs share is merged by whichever of them finishes last: every
+                   // sharer stores its partial result and counts itself in; the one that finds the
+                   // count complete reads all of them back and stores O.  Nobody waits.
+};
+struct Segment {
+    int pair, b0, n_blocks, part, parts;
+};
+template <int MODE>
+struct SegmentIter {
+    int total_blocks, per, cursor, end;
+    bool done = false;
+    __device__ SegmentIter(int total_blocks_, int per_, int pairs) : total_blocks(total_blocks_), per(per_) {
+        cursor = static_cast<int>(blockIdx.x) * per;
+        end = min(cursor + per, pairs * total_blocks);
+    }
+    __device__ bool next(Segment &s) {
+        if (MODE == WHOLE) {
+            if (done) return false;
+            done = true;
+            s = {static_cast<int>(blockIdx.x), 0, total_blocks, 0, 1};
+            return total_blocks > 0;
+        } else if (MODE == SPLIT) {
+            if (done) return false;
+            done = true;
+            const int b0 = static_cast<int>(blockIdx.y) * per;
+            s = {static_cast<int>(blockIdx.x), b0, min(per, total_blocks - b0), static_cast<int>(blockIdx.y),
+                 static_cast<int>(gridDim.y)};
+            return s.n_blocks > 0;
+        } else {
+            if (cursor >= end) return false;
+            s.pair = cursor / total_blocks;
+            s.b0 = cursor - s.pair * total_blocks;
+            s.n_blocks = min(total_blocks - s.b0, end - cursor);
+            const int first = (s.pair * total_blocks) / per;
+            const int last = ((s.pair + 1) * total_blocks - 1) / per;
+            s.part = static_cast<int>(blockIdx.x) - first;
+            s.parts = last - first + 1;
+            cursor += s.n_blocks;
+            return true;
+        }
+    }
+};
+
+// `per`: K/V blocks per range (SPLIT) or units per CTA (BALANCED).  part_o / part_ml: partial
+// results, [range][nq] rows (SPLIT) or [pair][max_parts][256] rows (BALANCED); `counters`
+// (BALANCED): one word per 32-row group of every pair, zero between launches.
+template <int MODE>
 __global__ void __launch_bounds__(attn::NUM_THREADS, 1)
 attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                       const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, __nv_bfloat16 *__restrict__ O,
                       int64_t ldo, int nq, int nkv, float scale_log2, int *status,
-                      int blocks_per_split, float *__restrict__ part_o, float *__restrict__ part_ml) {
+                      int per, float *__restrict__ part_o, float *__restrict__ part_ml,
+                      int max_parts, int *__restrict__ counters) {
     using namespace attn;
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(
@@ -140,7 +234,8 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     unsigned char *sQ = smem;                               // [TILES] tiles
     unsigned char *sKV = smem + TILES * TILE_BYTES;         // [KV_SLOTS] tiles
     auto bar_at = [&](int offset) { return reinterpret_cast<uint64_t *>(smem + offset); };
-    uint64_t *q_full = bar_at(kLayout.q_full.offset);        // [1]
+    uint64_t *q_full = bar_at(kLayout.q_full.offset);        // [1] TMA -> MMA: the segment's Q tiles
+    uint64_t *q_empty = bar_at(kLayout.q_empty.offset);      // [1] MMA -> TMA: last Q K^T of the segment done
     uint64_t *kv_full = bar_at(kLayout.kv_full.offset);      // [KV_SLOTS]
     uint64_t *kv_empty = bar_at(kLayout.kv_empty.offset);    // [KV_SLOTS]
     uint64_t *s_full = bar_at(kLayout.s_full.offset);        // [2] MMA -> softmax t: S_t holds block j
@@ -150,17 +245,23 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + kLayout.tmem_slot.offset);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * (BM * TILES);
-    // K/V blocks [b0, b0 + n_blocks) are this CTA's; j below counts from b0
+#ifdef GB200_ATTN_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == GB200_ATTN_TRACE_CTA) {
+        g_attn_trace[24 * 64] = clock64();
+        g_attn_trace[25 * 64] = (long long)global_timer_ns();
+    }
+#endif
     const int total_blocks = (nkv + BN - 1) / BN;
-    const int b0 = SPLIT ? static_cast<int>(blockIdx.y) * blocks_per_split : 0;
-    const int n_blocks = SPLIT ? max(0, min(blocks_per_split, total_blocks - b0)) : total_blocks;
+    const int pairs = (nq + BM * TILES - 1) / (BM * TILES);
+    // Every role walks the same list of segments; barriers that complete once per K/V block, per
+    // ring slot or per segment take their phase from counters that run across segments.
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_q);
         prefetch_tmap(&tmap_k);
         prefetch_tmap(&tmap_v);
         mbar_init(q_full, 1);
+        mbar_init(q_empty, 1);
         for (int s = 0; s < KV_SLOTS; ++s) {
             mbar_init(&kv_full[s], 1);
             mbar_init(&kv_empty[s], 1);
@@ -185,25 +286,38 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // of the previous kernel of the stream; no global memory is touched before it has completed.
     pdl_launch_dependents();
     pdl_wait();
+#ifdef GB200_ATTN_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == GB200_ATTN_TRACE_CTA) g_attn_trace[24 * 64 + 1] = clock64();
+#endif
 
     if (warp == 9) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            mbar_expect_tx(q_full, TILES * TILE_BYTES);
-            for (int t = 0; t < TILES; ++t) {
-                tma_load_2d(sQ + t * TILE_BYTES, &tmap_q, 0, q0 + t * BM, q_full);
-                tma_load_2d(sQ + t * TILE_BYTES + CHUNK_BYTES, &tmap_q, 64, q0 + t * BM, q_full);
-            }
-            // ring order: K_0 V_0 K_1 V_1 ...
-            for (int u = 0; u < 2 * n_blocks; ++u) {
-                const int slot = u % KV_SLOTS;
-                const uint32_t ph = (u / KV_SLOTS) & 1;
-                if (!mbar_wait(&kv_empty[slot], ph ^ 1, status, 301)) break;
-                const CUtensorMap *tm = (u & 1) ? &tmap_v : &tmap_k;
-                unsigned char *dst = sKV + slot * TILE_BYTES;
-                mbar_expect_tx(&kv_full[slot], TILE_BYTES);
-                tma_load_2d(dst, tm, 0, (b0 + (u >> 1)) * BN, &kv_full[slot]);
-                tma_load_2d(dst + CHUNK_BYTES, tm, 64, (b0 + (u >> 1)) * BN, &kv_full[slot]);
+            SegmentIter<MODE> it(total_blocks, per, pairs);
+            Segment sg;
+            bool ok = true;
+            int ring = 0;   // ring units issued so far
+            for (int seg = 0; ok && it.next(sg); ++seg) {
+                const int q0 = sg.pair * (BM * TILES);
+                if (seg > 0 && !mbar_wait(q_empty, (seg - 1) & 1, status, 302)) break;
+                ATTN_TRACE(12, seg);
+                mbar_expect_tx(q_full, TILES * TILE_BYTES);
+                for (int t = 0; t < TILES; ++t) {
+                    tma_load_2d(sQ + t * TILE_BYTES, &tmap_q, 0, q0 + t * BM, q_full);
+                    tma_load_2d(sQ + t * TILE_BYTES + CHUNK_BYTES, &tmap_q, 64, q0 + t * BM, q_full);
+                }
+                // ring order: K_0 V_0 K_1 V_1 ...
+                for (int u = 0; u < 2 * sg.n_blocks; ++u, ++ring) {
+                    const int slot = ring % KV_SLOTS;
+                    const uint32_t ph = (ring / KV_SLOTS) & 1;
+                    if (!mbar_wait(&kv_empty[slot], ph ^ 1, status, 301)) { ok = false; break; }
+                    const CUtensorMap *tm = (u & 1) ? &tmap_v : &tmap_k;
+                    unsigned char *dst = sKV + slot * TILE_BYTES;
+                    mbar_expect_tx(&kv_full[slot], TILE_BYTES);
+                    tma_load_2d(dst, tm, 0, (sg.b0 + (u >> 1)) * BN, &kv_full[slot]);
+                    tma_load_2d(dst + CHUNK_BYTES, tm, 64, (sg.b0 + (u >> 1)) * BN, &kv_full[slot]);
+                    if (u == 0) ATTN_TRACE(13, seg);
+                }
             }
         }
     } else if (warp == 8) {
@@ -211,14 +325,19 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(BM, BN, 0);  // A, B both K-major
             constexpr uint32_t idesc_pv = umma_idesc_bf16(BM, D, 1);   // B (= V) is MN-major
-            bool ok = mbar_wait(q_full, 0, status, 303);
+            SegmentIter<MODE> it(total_blocks, per, pairs);
+            Segment sg;
+            bool ok = true;
+            int ring = 0;   // ring units consumed before this segment
+            int blk = 0;    // K/V blocks done before this segment (phase of p_half / sp_ready)
 
+            // u, j below count within the segment
             auto wait_kv = [&](int u) -> bool {
-                return mbar_wait(&kv_full[u % KV_SLOTS], (u / KV_SLOTS) & 1, status, 304);
+                return mbar_wait(&kv_full[(ring + u) % KV_SLOTS], ((ring + u) / KV_SLOTS) & 1, status, 304);
             };
             auto issue_qk = [&](int t, int j) {
                 const uint32_t q_addr = smem_u32(sQ + t * TILE_BYTES);
-                const uint32_t k_addr = smem_u32(sKV + ((2 * j) % KV_SLOTS) * TILE_BYTES);
+                const uint32_t k_addr = smem_u32(sKV + ((ring + 2 * j) % KV_SLOTS) * TILE_BYTES);
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = (ks / 4) * CHUNK_BYTES + (ks % 4) * 32;
@@ -228,7 +347,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 umma_commit(&s_full[t]);
             };
             auto issue_pv = [&](int t, int j, int half) {
-                const uint32_t v_addr = smem_u32(sKV + ((2 * j + 1) % KV_SLOTS) * TILE_BYTES);
+                const uint32_t v_addr = smem_u32(sKV + ((ring + 2 * j + 1) % KV_SLOTS) * TILE_BYTES);
 #pragma unroll
                 for (int ks = half * 4; ks < half * 4 + 4; ++ks) {
                     // A = P from TMEM: row = lane, 16 kv values = 8 columns of bf16 pairs.
@@ -241,36 +360,51 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 }
             };
 
-            if (ok && n_blocks > 0) ok = wait_kv(0);
-            if (ok && n_blocks > 0) {
+            for (int seg = 0; ok && it.next(sg); ++seg) {
+                const int n_blocks = sg.n_blocks;
+                // The first Q K^T of a segment may run while the softmax warps still read the
+                // previous segment's O: S is free (the tensor pipe runs in order), and the first
+                // P V waits for p_half, which the softmax warps reach only after their epilogue.
+                ATTN_TRACE(14, seg);
+                if (!mbar_wait(q_full, seg & 1, status, 303)) { ok = false; break; }
+                ATTN_TRACE(15, seg);
+                if (!wait_kv(0)) { ok = false; break; }
+                ATTN_TRACE(16, seg);
                 tc_fence_after();
                 issue_qk(0, 0);
                 issue_qk(1, 0);
-                umma_commit(&kv_empty[0]);
-            }
-            for (int j = 0; j < n_blocks && ok; ++j) {
-                if (!wait_kv(2 * j + 1)) { ok = false; break; }
-                const bool more = j + 1 < n_blocks;
-                if (more && !wait_kv(2 * j + 2)) { ok = false; break; }
-                for (int t = 0; t < TILES; ++t) {
-                    // the first half of P_t (kv 0-63) is announced while the softmax still works
-                    // on the second, so half of P_t V_j leaves the chain softmax -> PV -> QK
-                    if (!mbar_wait(&p_half[t], j & 1, status, 306)) { ok = false; break; }
-                    tc_fence_after();
-                    issue_pv(t, j, 0);
-                    if (!mbar_wait(&sp_ready[t], j & 1, status, 307)) { ok = false; break; }
-                    ATTN_TRACE(8 + 2 * t, j);
-                    tc_fence_after();
-                    issue_pv(t, j, 1);
-                    if (more)
-                        issue_qk(t, j + 1);   // completes after PV(t, j): tensor pipe is in order
-                    else
-                        umma_commit(&o_full[t]);
-                    ATTN_TRACE(9 + 2 * t, j);
+                ATTN_TRACE(17, seg);
+                umma_commit(&kv_empty[ring % KV_SLOTS]);
+                if (n_blocks == 1) umma_commit(q_empty);
+                for (int j = 0; j < n_blocks && ok; ++j) {
+                    if (!wait_kv(2 * j + 1)) { ok = false; break; }
+                    const bool more = j + 1 < n_blocks;
+                    if (more && !wait_kv(2 * j + 2)) { ok = false; break; }
+                    const uint32_t ph = (blk + j) & 1;
+                    for (int t = 0; t < TILES; ++t) {
+                        // the first half of P_t (kv 0-63) is announced while the softmax still works
+                        // on the second, so half of P_t V_j leaves the chain softmax -> PV -> QK
+                        if (!mbar_wait(&p_half[t], ph, status, 306)) { ok = false; break; }
+                        tc_fence_after();
+                        issue_pv(t, j, 0);
+                        if (!mbar_wait(&sp_ready[t], ph, status, 307)) { ok = false; break; }
+                        ATTN_TRACE(8 + 2 * t, blk + j);
+                        tc_fence_after();
+                        issue_pv(t, j, 1);
+                        if (more)
+                            issue_qk(t, j + 1);   // completes after PV(t, j): tensor pipe is in order
+                        else
+                            umma_commit(&o_full[t]);
+                        ATTN_TRACE(9 + 2 * t, blk + j);
+                    }
+                    if (!ok) break;
+                    umma_commit(&kv_empty[(ring + 2 * j + 1) % KV_SLOTS]);
+                    if (more) umma_commit(&kv_empty[(ring + 2 * j + 2) % KV_SLOTS]);
+                    // the segment's last Q K^T has been issued: Q may be replaced once it is done
+                    if (j + 2 == n_blocks) umma_commit(q_empty);
                 }
-                if (!ok) break;
-                umma_commit(&kv_empty[(2 * j + 1) % KV_SLOTS]);
-                if (more) umma_commit(&kv_empty[(2 * j + 2) % KV_SLOTS]);
+                ring += 2 * n_blocks;
+                blk += n_blocks;
             }
         }
     } else {
@@ -282,14 +416,21 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16);
         const uint32_t t_s = t_row + t * BN;
         const uint32_t t_o = t_row + 256 + t * D;
+        SegmentIter<MODE> it(total_blocks, per, pairs);
+        Segment sg;
+        bool ok = true;
+        int blk = 0;   // K/V blocks done before this segment (phase of s_full)
+        const OutRows out{O, ldo, nq};
+
+        for (int seg = 0; ok && it.next(sg); ++seg) {
+        const int n_blocks = sg.n_blocks, b0 = sg.b0;
         float m_used = -FLT_MAX;  // maximum the exponentials are taken against (log2 domain)
         float l = 0.0f;           // running row sum
-        bool ok = true;
 
         for (int j = 0; j < n_blocks && ok; ++j) {
             // s_full(j) also tells that P_t V_{j-1} has finished: the tensor pipe runs in order.
-            if (!mbar_wait(&s_full[t], j & 1, status, 308)) { ok = false; break; }
-            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 0, j);
+            if (!mbar_wait(&s_full[t], (blk + j) & 1, status, 308)) { ok = false; break; }
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 0, blk + j);
             tc_fence_after();
             const int valid = min(BN, nkv - (b0 + j) * BN);
 
@@ -329,7 +470,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             uint32_t buf[2][32];
             tmem_ld_32x32(t_s, buf[0]);
             m_blk *= scale_log2;  // scale > 0: the maximum commutes with the scaling
-            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 1, j);
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 1, blk + j);
             // Lazy rescale: keep the old reference maximum unless it has fallen behind by more
             // than the threshold, so that O is touched rarely.
             const bool grow = (m_blk - m_used) > RESCALE_THRESHOLD;
@@ -405,84 +546,149 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
             unpk2(sum2, sum_lo, sum_hi);
             const float sum = sum_lo + sum_hi;
             l += sum;
-            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 2, j);
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 2, blk + j);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sp_ready[t]);
-            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 3, j);
+            if (lane_group == 0 && lane == 0) ATTN_TRACE(4 * t + 3, blk + j);
         }
 
-        // ---- epilogue: O / l -> bf16 -> global ----
-        if (ok && n_blocks > 0) ok = mbar_wait(&o_full[t], 0, status, 310);
-        if (ok && n_blocks > 0) {
-            tc_fence_after();
-            const int row = q0 + t * BM + row_in_tile;
-            if (SPLIT) {
-                // partial result of this K/V range: O as accumulated (relative to m_used), m_used, l
-                if (row < nq) {
-                    const int64_t slot = static_cast<int64_t>(blockIdx.y) * nq + row;
-                    part_ml[2 * slot] = m_used;
-                    part_ml[2 * slot + 1] = l;
-                }
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_32x32(t_o + c * 32, o);
-                    tmem_ld_wait();
-                    if (row < nq) {
-                        float4 *dst = reinterpret_cast<float4 *>(
-                            part_o + (static_cast<int64_t>(blockIdx.y) * nq + row) * D + c * 32);
-#pragma unroll
-                        for (int q = 0; q < 8; ++q)
-                            dst[q] = make_float4(__uint_as_float(o[4 * q]), __uint_as_float(o[4 * q + 1]),
-                                                 __uint_as_float(o[4 * q + 2]), __uint_as_float(o[4 * q + 3]));
-                    }
-                }
-            } else {
+        blk += n_blocks;
+
+        // ---- epilogue: O / l -> bf16 -> global, or the segment's partial result ----
+        if (lane_group == 0 && lane == 0) ATTN_TRACE(18 + 3 * t, seg);
+        // A pair shared with other CTAs (BALANCED): partial results lie per warp as
+        // [part][column][lane] (a warp's store or load of one column is one 128-byte line);
+        // whichever sharer finds all the others counted in merges them with its own O, which is
+        // still in TMEM.  The last segment of a run is usually that sharer (the others were first
+        // segments of their CTAs): it looks at the count while its last P V is still running.
+        const bool shared = (MODE == BALANCED) && sg.parts > 1;
+        const int others = sg.parts - 1;
+        const int group = (sg.pair * TILES + t) * 4 + lane_group;          // 32 rows of the pair
+        int *counter = counters + group;
+        auto ml_at = [&](int k) { return part_ml + 2 * ((static_cast<int64_t>(group) * max_parts + k) * 32 + lane); };
+        auto o_at = [&](int k) { return part_o + (static_cast<int64_t>(group) * max_parts + k) * (32 * D) + lane; };
+        int seen = -1;
+        if (shared && it.cursor >= it.end) {
+            if (lane == 0) asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            seen = __shfl_sync(0xffffffffu, seen, 0);
+            __syncwarp();
+        }
+        if (ok) ok = mbar_wait(&o_full[t], seg & 1, status, 310);
+        if (!ok) break;
+        if (lane_group == 0 && lane == 0) ATTN_TRACE(19 + 3 * t, seg);
+        tc_fence_after();
+        const int row = sg.pair * (BM * TILES) + t * BM + row_in_tile;
+        if (MODE == WHOLE || (MODE == BALANCED && sg.parts == 1)) {
             const float inv = 1.0f / l;
-            const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(O) & 15) == 0);
-            const bool vec32_ok = (ldo % 16 == 0) && ((reinterpret_cast<uintptr_t>(O) & 31) == 0);
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld_32x32(t_o + c * 32, o);
+                tmem_ld_wait();
+                out.store_chunk(row, c, o, inv);
+            }
+        } else if (MODE == SPLIT) {
+            // partial result of this K/V range: O as accumulated (relative to m_used), m_used, l
+            const int64_t slot = static_cast<int64_t>(sg.part) * nq + row;
+            if (row < nq) *reinterpret_cast<float2 *>(part_ml + 2 * slot) = make_float2(m_used, l);
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32(t_o + c * 32, o);
                 tmem_ld_wait();
                 if (row < nq) {
-                    __nv_bfloat16 *dst = O + static_cast<int64_t>(row) * ldo + c * 32;
-                    if (vec32_ok) {
+                    float4 *dst = reinterpret_cast<float4 *>(part_o + slot * D + c * 32);
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                w[i] = pack_bf16(__uint_as_float(o[16 * h + 2 * i]) * inv,
-                                                 __uint_as_float(o[16 * h + 2 * i + 1]) * inv);
-                            st_global_256(dst + 16 * h, w[0], w[1], w[2], w[3], w[4], w[5], w[6], w[7]);
-                        }
-                    } else if (vec_ok) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint4 v;
-                            v.x = pack_bf16(__uint_as_float(o[8 * q + 0]) * inv, __uint_as_float(o[8 * q + 1]) * inv);
-                            v.y = pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv);
-                            v.z = pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv);
-                            v.w = pack_bf16(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv);
-                            *reinterpret_cast<uint4 *>(dst + 8 * q) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            dst[i] = __float2bfloat16_rn(__uint_as_float(o[i]) * inv);
-                    }
+                    for (int q = 0; q < 8; ++q)
+                        dst[q] = make_float4(__uint_as_float(o[4 * q]), __uint_as_float(o[4 * q + 1]),
+                                             __uint_as_float(o[4 * q + 2]), __uint_as_float(o[4 * q + 3]));
                 }
             }
+        } else {
+            if (seen != others) {
+                *reinterpret_cast<float2 *>(ml_at(sg.part)) = make_float2(m_used, l);
+                float *dst = o_at(sg.part);
+#pragma unroll 1
+                for (int c = 0; c < 4; c += 2) {
+                    uint32_t o[2][32];
+                    tmem_ld_32x32(t_o + c * 32, o[0]);
+                    tmem_ld_32x32(t_o + c * 32 + 32, o[1]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) dst[(c * 32 + i) * 32] = __uint_as_float(o[i >> 5][i & 31]);
+                }
+                // the warp's stores, then one release that counts it in
+                __syncwarp();
+                if (lane == 0)
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(seen) : "l"(counter) : "memory");
+                seen = __shfl_sync(0xffffffffu, seen, 0);
+                __syncwarp();
+            }
+            if (seen == others) {
+                if (lane == 0) *counter = 0;   // as the next launch expects it
+                // reference maximum over all parts
+                float m_all = m_used;
+#pragma unroll 4
+                for (int kk = 0; kk < others; ++kk) m_all = fmaxf(m_all, __ldcg(ml_at(kk + (kk >= sg.part))));
+                // This CTA's own part from TMEM first, then steps (column chunk c, other part kk),
+                // the loads of a step in flight while the step before it is added up.  (The sums
+                // start from the merging sharer's part, so their last bit can depend on which sharer
+                // merges: normally the one whose part ends its CTA's run.)
+                const float w_own = fast_exp2(m_used - m_all);
+                float l_all = w_own * l;
+                float inv = 0.0f;
+                const int n_steps = 4 * others;                      // even
+                float buf[2][32];
+                float2 ml_buf[2];
+                auto fetch = [&](int step, float(&v)[32], float2 &ml) {
+                    const int c = step / others, kk = step - c * others, k = kk + (kk >= sg.part);
+                    ml = __ldcg(reinterpret_cast<const float2 *>(ml_at(k)));
+                    const float *src = o_at(k) + c * 32 * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __ldcg(src + i * 32);
+                };
+                uint32_t o[32];
+                auto add_up = [&](int step, const float(&v)[32], const float2 &ml) {
+                    const int c = step / others, kk = step - c * others;
+                    const float w = fast_exp2(ml.x - m_all);
+                    if (kk == 0) {
+                        tmem_ld_32x32(t_o + c * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * w_own);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(fmaf(w, v[i], __uint_as_float(o[i])));
+                    if (c == 0) l_all = fmaf(w, ml.y, l_all);
+                    if (kk == others - 1) {
+                        if (c == 0) inv = 1.0f / l_all;
+                        out.store_chunk(row, c, o, inv);
+                    }
+                };
+                fetch(0, buf[0], ml_buf[0]);
+#pragma unroll 1
+                for (int step = 0; step < n_steps; step += 2) {
+                    fetch(step + 1, buf[1], ml_buf[1]);
+                    add_up(step, buf[0], ml_buf[0]);
+                    if (step + 2 < n_steps) fetch(step + 2, buf[0], ml_buf[0]);
+                    add_up(step + 1, buf[1], ml_buf[1]);
+                }
             }
         }
+        if (lane_group == 0 && lane == 0) ATTN_TRACE(20 + 3 * t, seg);
+        }   // segments
     }
 
     tc_fence_before();
     __syncthreads();
+#ifdef GB200_ATTN_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == GB200_ATTN_TRACE_CTA) {
+        g_attn_trace[26 * 64] = clock64();
+        g_attn_trace[27 * 64] = (long long)global_timer_ns();
+    }
+#endif
     if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, attn::TMEM_COLS);
@@ -541,11 +747,20 @@ int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void
 #ifndef GB200_ATTN_AUTO_PAIR
 #define GB200_ATTN_AUTO_PAIR 0
 #endif
+// Equal runs per CTA are chosen when the longest CTA's walk plus this allowance (in K/V blocks)
+// comes to at most this share of the whole-pair schedule's.
+#ifndef GB200_ATTN_BALANCED_GAIN_PCT
+#define GB200_ATTN_BALANCED_GAIN_PCT 97
+#endif
+#ifndef GB200_ATTN_BALANCED_COST_BLOCKS
+#define GB200_ATTN_BALANCED_COST_BLOCKS 3
+#endif
 
 // kernel_choice: 0 = pick, 1 = one CTA per two Q tiles, 2 = CTA pairs with two Q tiles per CTA
 // (attention_pair.cu).
-// kv_splits: 0 = pick (split the K/V range when the Q tiles alone leave more than half of the SMs
-// idle), 1 = never split, n > 1 = that many ranges (fewer if there are not enough K/V blocks).
+// kv_splits: 0 = pick, 1 = every CTA walks all K/V blocks of its Q tiles, n > 1 = that many K/V
+// ranges merged by a second kernel (fewer if there are not enough blocks), -1 = equal runs of
+// (Q tile pair, K/V block) units per CTA, merged inside the kernel.
 int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                        const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq, int64_t nkv,
                        int64_t d, float scale, cudaStream_t stream, int kernel_choice = 0, int kv_splits = 0) {
@@ -568,25 +783,56 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     const float scale_log2 = scale * 1.4426950408889634f;
     const unsigned grid = (unsigned)((nq + BM * TILES - 1) / (BM * TILES));
     const int total_blocks = (int)((nkv + BN - 1) / BN);
+    const int sms = ctx->sm_count;
     int splits = kv_splits;
     if (splits == 0) {
-        // One CTA per two Q tiles fills the GPU from 74 CTAs up.  Below that, K/V ranges of at
-        // least two blocks go to the idle SMs; the combine pass costs one read of the partials.
         splits = 1;
-        if ((int)grid * 2 <= ctx->sm_count && total_blocks >= 4) {
-            splits = ctx->sm_count / (int)grid;
+        const int64_t units = (int64_t)grid * total_blocks;
+        const int64_t whole_time = (int64_t)((grid + sms - 1) / sms) * total_blocks;   // in K/V blocks
+        const int64_t balanced_time = (units + sms - 1) / sms;
+        if ((int)grid * 2 <= sms && total_blocks >= 4) {
+            // Few Q tiles: K/V ranges of at least two blocks go to the idle SMs; the combine pass
+            // costs one read of the partials.
+            splits = sms / (int)grid;
             if (splits > total_blocks / 2) splits = total_blocks / 2;
+        } else if ((balanced_time + GB200_ATTN_BALANCED_COST_BLOCKS) * 100 <= whole_time * GB200_ATTN_BALANCED_GAIN_PCT) {
+            // The last wave of whole pairs would leave SMs idle: equal runs.  Handing a pair over
+            // inside a CTA and merging the shared pairs at the end (all CTAs at once, bound by the
+            // L2) cost about three K/V blocks' time: 128 pairs x 32 blocks on 148 SMs gain little
+            // (measured 68.6 against 69.7 us), 157 pairs x 32 blocks take 80 instead of 135 us and
+            // 128 pairs x 128 blocks 230 instead of 262 us.
+            splits = -1;
         }
     }
     if (splits > total_blocks) splits = total_blocks;
-    if (splits <= 1) {
-        rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<false>, SMEM_BYTES);
+    if (splits == -1 && (int64_t)grid * total_blocks > (int64_t)1 << 30) splits = 1;
+    if (splits == 1 || splits == 0) {
+        rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<WHOLE>, SMEM_BYTES);
         if (rc) return rc;
-        GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<false>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+        GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<WHOLE>, dim3(grid), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
                                   stream, tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv,
                                   scale_log2, ctx->d_status, 0, static_cast<float *>(nullptr),
-                                  static_cast<float *>(nullptr)));
+                                  static_cast<float *>(nullptr), 0, static_cast<int *>(nullptr)));
         return after_launch(ctx, "attention_bf16_kernel");
+    }
+    if (splits == -1) {
+        const int64_t units = (int64_t)grid * total_blocks;
+        const int per = (int)((units + sms - 1) / sms);
+        const unsigned ctas = (unsigned)((units + per - 1) / per);
+        const int max_parts = (total_blocks + per - 1) / per + 1;
+        const size_t rows = (size_t)grid * max_parts * (BM * TILES);
+        rc = workspace_reserve(ctx, rows * (D + 2) * sizeof(float));
+        if (rc) return rc;
+        rc = merge_counters_reserve(ctx, (size_t)grid * TILES * 4);
+        if (rc) return rc;
+        float *part_o = static_cast<float *>(ctx->workspace);
+        float *part_ml = part_o + rows * D;
+        rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<BALANCED>, SMEM_BYTES);
+        if (rc) return rc;
+        GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<BALANCED>, dim3(ctas), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
+                                  stream, tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo, (int)nq, (int)nkv,
+                                  scale_log2, ctx->d_status, per, part_o, part_ml, max_parts, ctx->merge_counters));
+        return after_launch(ctx, "attention_bf16_kernel<balanced>");
     }
     const int per = (total_blocks + splits - 1) / splits;
     splits = (total_blocks + per - 1) / per;          // every range holds at least one block
@@ -594,11 +840,12 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
     if (rc) return rc;
     float *part_o = static_cast<float *>(ctx->workspace);
     float *part_ml = part_o + (size_t)splits * (size_t)nq * D;
-    rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<true>, SMEM_BYTES);
+    rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<SPLIT>, SMEM_BYTES);
     if (rc) return rc;
-    GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<true>, dim3(grid, (unsigned)splits), dim3(NUM_THREADS),
+    GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<SPLIT>, dim3(grid, (unsigned)splits), dim3(NUM_THREADS),
                               (size_t)SMEM_BYTES, stream, tq, tk, tv, static_cast<__nv_bfloat16 *>(O), ldo,
-                              (int)nq, (int)nkv, scale_log2, ctx->d_status, per, part_o, part_ml));
+                              (int)nq, (int)nkv, scale_log2, ctx->d_status, per, part_o, part_ml, 0,
+                              static_cast<int *>(nullptr)));
     rc = after_launch(ctx, "attention_bf16_kernel<split>");
     if (rc) return rc;
     GB200_CUDA_TRY(launch_pdl(attention_combine_kernel, dim3((unsigned)((nq + 7) / 8)), dim3(256), 0, stream,
@@ -624,7 +871,7 @@ static int check_attention_args(const void *Q, int64_t ldq, const void *K, int64
     return GB200_OK;
 }
 
-int kernel_regs_attention() { return kernel_registers(attention_bf16_kernel<false>); }
+int kernel_regs_attention() { return kernel_registers(attention_bf16_kernel<WHOLE>); }
 
 }  // namespace gb200
 
@@ -660,7 +907,7 @@ int gb200_attention_bf16_cluster(gb200_ctx *ctx, const void *Q, int64_t ldq, con
 
 #ifdef GB200_ATTN_TRACE
 int gb200_attn_trace_read(long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 16 * 64);
+    return (int)cudaMemcpyFromSymbol(out, g_attn_trace, sizeof(long long) * 28 * 64);
 }
 #endif
 
@@ -678,15 +925,16 @@ int gb200_attention_bf16_variant(gb200_ctx *ctx, const void *Q, int64_t ldq, con
                               static_cast<cudaStream_t>(stream), variant);
 }
 
-// Test / benchmark hook: the single-CTA kernel with the number of K/V ranges chosen by the caller
-// (1 = no split, 0 = let the library pick).
+// Test / benchmark hook: the single-CTA kernel with the schedule chosen by the caller (0 = let the
+// library pick, 1 = whole pairs, n > 1 = that many K/V ranges and a combine pass, -1 = equal runs
+// per CTA merged inside the kernel).
 int gb200_attention_bf16_splitkv(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                                  const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                                  int64_t nkv, int64_t d, float scale, void *stream, int splits) {
     DeviceScope scope;
     int rc = scope.enter(ctx);
     if (rc) return rc;
-    GB200_REQUIRE(splits >= 0 && splits <= 1024, GB200_ERR_INVALID_ARG, "splits out of range");
+    GB200_REQUIRE(splits >= -1 && splits <= 1024, GB200_ERR_INVALID_ARG, "splits out of range");
     rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
     if (rc) return rc < 0 ? rc : GB200_OK;
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,

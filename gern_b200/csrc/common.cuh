@@ -87,6 +87,10 @@ struct gb200_ctx {
     // scratch of kernels that need global memory beyond their operands (split-K slabs)
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
+    // arrival counters of kernels whose thread blocks merge partial results among themselves;
+    // zero whenever no such kernel is running (the merging block puts its counter back)
+    int *merge_counters = nullptr;
+    size_t merge_counter_words = 0;
     cudaStream_t copy_stream[2] = {nullptr, nullptr};
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
 };
@@ -140,6 +144,8 @@ inline int kernel_registers(Kernel kernel) {
 int stage_reserve(gb200_ctx *ctx, int slot, size_t bytes);
 // Grows the context's kernel workspace to at least `bytes`.
 int workspace_reserve(gb200_ctx *ctx, size_t bytes);
+// Grows the context's zeroed arrival counters to at least `words`.
+int merge_counters_reserve(gb200_ctx *ctx, size_t words);
 // Checks the launch that was just issued and counts it.
 int after_launch(gb200_ctx *ctx, const char *what);
 

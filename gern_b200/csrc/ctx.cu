@@ -47,6 +47,8 @@ int host_finish(gb200_ctx *ctx, cudaStream_t s0, cudaStream_t s1) {
     if (*ctx->h_status != 0) {
         const int st = *ctx->h_status;
         cudaMemsetAsync(ctx->d_status, 0, sizeof(int), s0);
+        // a kernel that gave up may have left arrival counters half way
+        if (ctx->merge_counters) cudaMemsetAsync(ctx->merge_counters, 0, ctx->merge_counter_words * sizeof(int), s0);
         cudaStreamSynchronize(s0);
         set_error("a kernel gave up a bounded wait (status code %d); the result is not valid", st);
         return GB200_ERR_TIMEOUT;
@@ -86,6 +88,19 @@ int workspace_reserve(gb200_ctx *ctx, size_t bytes) {
     }
     GB200_CUDA_TRY(cudaMalloc(&ctx->workspace, bytes));
     ctx->workspace_bytes = bytes;
+    return GB200_OK;
+}
+
+int merge_counters_reserve(gb200_ctx *ctx, size_t words) {
+    if (ctx->merge_counter_words >= words) return GB200_OK;
+    if (ctx->merge_counters) {
+        GB200_CUDA_TRY(cudaFree(ctx->merge_counters));
+        ctx->merge_counters = nullptr;
+        ctx->merge_counter_words = 0;
+    }
+    GB200_CUDA_TRY(cudaMalloc(&ctx->merge_counters, words * sizeof(int)));
+    GB200_CUDA_TRY(cudaMemset(ctx->merge_counters, 0, words * sizeof(int)));
+    ctx->merge_counter_words = words;
     return GB200_OK;
 }
 
@@ -233,6 +248,7 @@ int gb200_ctx_destroy(gb200_ctx *ctx) {
     for (int i = 0; i < 4; ++i)
         if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
     if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->merge_counters) cudaFree(ctx->merge_counters);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     delete ctx;
@@ -248,6 +264,7 @@ int gb200_device_sync(gb200_ctx *ctx) {
     GB200_CUDA_TRY(cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (st != 0) {
         cudaMemset(ctx->d_status, 0, sizeof(int));
+        if (ctx->merge_counters) cudaMemset(ctx->merge_counters, 0, ctx->merge_counter_words * sizeof(int));
         set_error("a kernel gave up a bounded wait (status code %d)", st);
         return GB200_ERR_TIMEOUT;
     }

@@ -99,7 +99,7 @@ constexpr Gemm2CtaLayout gemm_2cta_layout(int stages_n) {
 struct AttentionLayout {
     static constexpr int kTiles = 2, kKvSlots = 5, kTileBytes = 128 * 128 * 2, kTmemColumns = 512, kCluster = 1;
     int threads = 320;
-    Region q, kv, q_full, kv_full, kv_empty, s_full, sp_ready, o_full, p_half, tmem_slot;
+    Region q, kv, q_full, q_empty, kv_full, kv_empty, s_full, sp_ready, o_full, p_half, tmem_slot;
     int dynamic_bytes = 0;
 };
 constexpr AttentionLayout attention_layout(int threads) {
@@ -109,6 +109,7 @@ constexpr AttentionLayout attention_layout(int threads) {
     l.q = p.tiles(AttentionLayout::kTiles, AttentionLayout::kTileBytes);
     l.kv = p.tiles(AttentionLayout::kKvSlots, AttentionLayout::kTileBytes);
     l.q_full = p.barriers(1);
+    l.q_empty = p.barriers(1);
     l.kv_full = p.barriers(AttentionLayout::kKvSlots);
     l.kv_empty = p.barriers(AttentionLayout::kKvSlots);
     l.s_full = p.barriers(AttentionLayout::kTiles);

@@ -20,7 +20,8 @@
  *     to the device, run the same kernels, copy the result back and return after the result
  *     is in host memory.
  *   - A context owns one scratch workspace (split-K slabs of the bf16 GEMM, split copies of the
- *     fp32 matmul's operands) and one set of staging buffers: calls on the same context whose
+ *     fp32 matmul's operands, partial results of the GEMM -> softmax -> GEMM chain) and one set
+ *     of staging buffers: calls on the same context whose
  *     kernels could overlap on the GPU (different streams) must use different contexts, as
  *     Gern's single-stream hooks never overlap (src/codegen/codegen.cpp:576-611).
  *   - Status: 0 = success; negative = failure (see gb200_status).  A human-readable message
@@ -199,9 +200,13 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
  * all row-major; S and P stay in TMEM / shared memory.  d must be 128 in this build.  The
  * nearest reference analogue is the chained-GEMM fusion with a per-tile temporary
  * (test/test-cpu-mm.cpp:266-408).  `scale` must be positive and finite (the row maximum is taken
- * before scaling); anything else is refused with GB200_ERR_INVALID_ARG.  When nq is too small to
- * give every SM a pair of Q tiles, the K/V range is cut across thread blocks and a second kernel
- * merges the partial results (kept in the context's workspace). */
+ * before scaling); anything else is refused with GB200_ERR_INVALID_ARG.  Work is dealt out in
+ * pairs of 128-row Q tiles.  When nq is too small to give every SM a pair, the K/V range is cut
+ * across thread blocks and a second kernel merges the partial results.  When whole pairs would
+ * leave SMs idle in their last round (157 pairs on 148 SMs), the (pair, K/V block) units are dealt
+ * out in equal runs instead, and a pair shared by several thread blocks is merged inside the
+ * kernel by the one that finishes last; the last bit of such a row can then depend on which
+ * block merged.  Partial results live in the context's workspace either way. */
 int gb200_attention_bf16(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                          const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                          int64_t nkv, int64_t d, float scale, void *stream);

@@ -112,10 +112,7 @@ def test_against_reference_chain_fixture(ctx, golden, golden_maker):
 def test_full_size_sampled(ctx, oracle):
     nq, nkv = 32768, 4096
     q, k, v = make(nq, nkv, 0)
-    o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
     scale = 1.0 / np.sqrt(128.0)
-    ctx.attention_bf16(q, k, v, o, scale)
-    ctx.sync()
     # two rows of every 128-row Q tile (so both tiles of every CTA, first and last CTA included),
     # at lanes that move through the tile, plus one whole tile
     idx = sorted({t * 128 + (t * 53) % 128 for t in range(nq // 128)} | {t * 128 + (t * 29 + 64) % 128 for t in range(nq // 128)}
@@ -124,17 +121,27 @@ def test_full_size_sampled(ctx, oracle):
     oracle.set_threads(oracle.max_threads())
     want = oracle.attention_bf16(bits(q[sel]), bits(k), bits(v), scale)
     oracle.set_threads(1)
-    got = o[sel].float().cpu().numpy()
-    assert frob(got, want) <= 1e-2
-    # and row by row, so that one bad row cannot hide in the norm of 640
-    err = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
-    assert err.max() <= 2e-2, (idx[int(err.argmax())], float(err.max()))
-    # rows are independent: any row block alone gives the same bits (with the K/V range left whole,
-    # as in the full-size run; a small problem would otherwise have its range split across CTAs)
+    outs = {}
+    # 1: every CTA walks the whole K/V range of its pair (what the library picks at this size);
+    # -1: equal runs per CTA, the shared pairs merged inside the kernel
+    for splits in (1, -1):
+        o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+        ctx.attention_bf16(q, k, v, o, scale, splits=splits)
+        ctx.sync()
+        got = o[sel].float().cpu().numpy()
+        assert frob(got, want) <= 1e-2, splits
+        # and row by row, so that one bad row cannot hide in the norm of 640
+        err = np.linalg.norm(got - want, axis=1) / np.linalg.norm(want, axis=1)
+        assert err.max() <= 2e-2, (splits, idx[int(err.argmax())], float(err.max()))
+        outs[splits] = o
+    # the two schedules differ by fp32 reassociation and one bf16 rounding, on every row
+    diff = (outs[-1].float() - outs[1].float()).norm(dim=1) / outs[1].float().norm(dim=1)
+    assert float(diff.max()) <= 1e-2
+    # rows are independent: any row block alone gives the same bits (with the K/V range left whole)
     o2 = torch.zeros((256, 128), dtype=torch.bfloat16, device="cuda")
     ctx.attention_bf16(q[1024:1280].contiguous(), k, v, o2, scale, splits=1)
     ctx.sync()
-    assert torch.equal(o2, o[1024:1280])
+    assert torch.equal(o2, outs[1][1024:1280])
 
 
 def test_host_entry_point(ctx, oracle):
@@ -208,6 +215,55 @@ def test_split_output_with_a_padded_pitch(ctx, oracle):
     want = oracle.attention_bf16(bits(q), bits(k), bits(v), 0.1)
     assert frob(o[:, :128].float().cpu().numpy(), want) <= 1e-2
     assert bool((o[:, 128:] == 3.0).all())
+
+
+@pytest.mark.parametrize("nq,nkv", [(2048, 1024),      # 8 pairs x 8 blocks on 148 SMs: one block per CTA, 8 sharers per pair
+                                    (5000, 3000),      # ragged rows and a ragged last block: runs of 4 of 24 blocks
+                                    (40000, 1100),     # runs longer than a pair: whole pairs and shared ones in one CTA
+                                    (300, 128),        # one block: nothing to share
+                                    (38000, 2048)])    # 149 pairs: a second wave of whole pairs avoided
+def test_equal_runs_merged_inside_the_kernel(ctx, oracle, nq, nkv):
+    """splits = -1: the (Q tile pair, K/V block) units are dealt out in equal runs, one per CTA; a
+    pair shared by several CTAs is merged by the one that finishes last.  Checked against the
+    whole-pair schedule on every row, against the oracle on sampled rows, and launched twice so
+    that the arrival counters are seen to come back to zero."""
+    q, k, v = make(nq, nkv, nq + nkv)
+    scale = 1.0 / np.sqrt(128.0)
+    o1 = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+    ctx.attention_bf16(q, k, v, o1, scale, splits=1)
+    outs = []
+    for _ in range(2):
+        o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+        ctx.attention_bf16(q, k, v, o, scale, splits=-1)
+        outs.append(o)
+    ctx.sync()
+    for o in outs:
+        diff = (o.float() - o1.float()).norm(dim=1) / o1.float().norm(dim=1)
+        assert float(diff.max()) <= 1e-2
+    # the same sharer normally merges on every launch; if another one did, the sums differ in their last bit
+    a, b = outs[0].float(), outs[1].float()
+    assert bool(((a - b).abs() <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-30).all())
+    idx = sorted({(i * 9973) % nq for i in range(96)} | {0, nq - 1})
+    sel = torch.tensor(idx, device="cuda")
+    oracle.set_threads(oracle.max_threads())
+    want = oracle.attention_bf16(bits(q[sel]), bits(k), bits(v), scale)
+    oracle.set_threads(1)
+    assert frob(outs[1][sel].float().cpu().numpy(), want) <= 1e-2
+
+
+def test_equal_runs_after_a_different_shape_and_with_a_padded_pitch(ctx, oracle):
+    """The counters and the partial-result workspace are shared by all launches of a context."""
+    scale = 0.1
+    for nq, nkv in ((2048, 1024), (700, 2500), (2048, 1024)):
+        q, k, v = make(nq, nkv, nq)
+        o = torch.full((nq, 130), 3.0, dtype=torch.bfloat16, device="cuda")     # rows not 8-byte aligned
+        ctx.attention_bf16(q, k, v, o[:, :128], scale, splits=-1)
+        ctx.sync()
+        oracle.set_threads(oracle.max_threads())
+        want = oracle.attention_bf16(bits(q[:256]), bits(k), bits(v), scale)
+        oracle.set_threads(1)
+        assert frob(o[:256, :128].float().cpu().numpy(), want) <= 1e-2
+        assert bool((o[:, 128:] == 3.0).all())
 
 
 def test_cluster_entry_point(ctx, oracle):
