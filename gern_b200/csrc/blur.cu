@@ -179,6 +179,19 @@ blur3x3_tma_kernel(const __grid_constant__ CUtensorMap in_map, float *__restrict
 #ifndef GB200_BLUR_STCS
 #define GB200_BLUR_STCS 0
 #endif
+#ifdef GB200_BLUR_TRACE
+// Debug-only timeline (compiled out of the library), %globaltimer nanoseconds.  Thread 0 of the
+// first block of the grid (with a halo: the block row that reads it) fills [0..3]: entry, previous
+// kernel complete, loads returned, stores issued; thread 0 of the first block of the next block
+// row fills [4..7]; [8] = latest "stores issued" over all blocks, [9] = earliest entry.
+__device__ unsigned long long g_blur_trace[16];
+__device__ __forceinline__ unsigned long long blur_now() { return global_timer_ns(); }
+__device__ __forceinline__ unsigned long long blur_now_after(float v) {
+    unsigned long long t;
+    asm volatile("{\n\t.reg .f32 z;\n\tmov.f32 z, %1;\n\tmov.u64 %0, %%globaltimer;\n\t}" : "=l"(t) : "f"(v) : "memory");
+    return t;
+}
+#endif
 template <int ROWS>
 __global__ void __launch_bounds__(128)
 blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
@@ -192,10 +205,18 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
     const int nbx = (out_cols + 511) / 512;
     const int bx = blockIdx.x % nbx, by_lin = blockIdx.x / nbx, nby = gridDim.x / nbx;
     const int c0 = (bx * 128 + threadIdx.x) * 4;
+#ifdef GB200_BLUR_TRACE
+    const int trace_slot = (threadIdx.x == 0 && blockIdx.x == 0) ? 0 : (threadIdx.x == 0 && blockIdx.x == nbx) ? 4 : -1;
+    const unsigned long long t_entry = blur_now();
+    if (trace_slot >= 0) g_blur_trace[trace_slot] = t_entry;
+#endif
     // Launched with programmatic stream serialisation: blocks may become resident while the
     // previous kernel of the stream drains; nothing is read before that kernel has completed.
     pdl_launch_dependents();
     pdl_wait();
+#ifdef GB200_BLUR_TRACE
+    if (trace_slot >= 0) g_blur_trace[trace_slot + 1] = blur_now();
+#endif
     if (c0 >= out_cols) return;
     // With a halo the block rows run bottom-up, so that the few blocks that read the (possibly
     // remote, high-latency) halo rows start first and finish under the rest of the kernel.
@@ -230,6 +251,14 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
                 b[r] = *reinterpret_cast<const float2 *>(rp + 4);
             }
         }
+#ifdef GB200_BLUR_TRACE
+        if (trace_slot >= 0) {
+            float dep = 0.0f;
+#pragma unroll
+            for (int r = 0; r < ROWS + 2; ++r) dep += a[r].x + b[r].y;
+            g_blur_trace[trace_slot + 2] = blur_now_after(dep);
+        }
+#endif
         uint64_t ta[ROWS + 2], tb[ROWS + 2];
 #pragma unroll
         for (int r = 0; r < ROWS + 2; ++r) hpass4(a[r], b[r], ta[r], tb[r]);
@@ -257,6 +286,9 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
             float v[6];
 #pragma unroll
             for (int k = 0; k < 6; ++k) v[k] = (c0 + k < in_cols) ? rp[k] : 0.0f;
+#ifdef GB200_BLUR_TRACE
+            if (trace_slot >= 0 && r == n_out + 1) g_blur_trace[trace_slot + 2] = blur_now_after(v[0] + v[5]);
+#endif
             uint64_t ta, tb;
             hpass4(make_float4(v[0], v[1], v[2], v[3]), make_float2(v[4], v[5]), ta, tb);
             if (r >= 2)
@@ -265,6 +297,13 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
             t0a = t1a; t0b = t1b; t1a = ta; t1b = tb;
         }
     }
+#ifdef GB200_BLUR_TRACE
+    {
+        const unsigned long long t_end = blur_now();
+        if (trace_slot >= 0) g_blur_trace[trace_slot + 3] = t_end;
+        if (threadIdx.x == 0 && (blockIdx.x & 63) == 0) atomicMax(&g_blur_trace[8], t_end);
+    }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------
@@ -460,6 +499,17 @@ int blur_dispatch(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_row
 using namespace gb200;
 
 extern "C" {
+
+#ifdef GB200_BLUR_TRACE
+// Debug builds only: copies the timeline out and resets it for the next launch.
+int gb200_blur_trace_read(unsigned long long *out) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, gb200::g_blur_trace, sizeof(unsigned long long) * 16);
+    unsigned long long init[16] = {0};
+    init[9] = ~0ull;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(gb200::g_blur_trace, init, sizeof(init));
+    return (int)e;
+}
+#endif
 
 int gb200_blur3x3_f32(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
                       int64_t in_cols, float *out, int64_t out_ld, void *stream) {
