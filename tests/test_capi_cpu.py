@@ -76,3 +76,13 @@ def test_kernel_resources_come_from_the_planned_layouts():
     with pytest.raises(api.GernB200Error) as e:
         api.kernel_resources("no_such_kernel")
     assert e.value.code == -1
+
+
+def test_timeline_tool_imports_and_shipped_library_has_no_trace_code():
+    """gern_b200.timeline builds its own debug libraries; the shipped one exports no trace reader."""
+    import ctypes
+    from gern_b200 import timeline, build
+    assert timeline.OUT_DIR.startswith(os.path.join(build.ROOT, "build"))
+    lib = ctypes.CDLL(build.LIB_PATH)
+    for name in ("gb200_attn_trace_read", "gb200_blur_trace_read"):
+        assert not hasattr(lib, name)
