@@ -228,9 +228,11 @@ class BlurWorkload(Workload):
         self.transport = "none"
         g = torch.Generator(device="cuda").manual_seed(1234 + rank)
         if world > 1:
-            # Preferred: the band lives in symmetric memory, and the kernel reads the two halo
-            # rows straight out of the next rank's band over NVLink (plain loads, no collective
-            # and no extra launch).  Fallback: NCCL send/recv into a local halo buffer each step.
+            # Preferred: the band lives in symmetric memory and the library is handed the address
+            # of the next rank's first two rows; every step it has a copy engine fetch them over
+            # NVLink into a local slot that the kernel's last block row waits for (no collective,
+            # no extra launch, and the kernel itself reads local memory only).  Fallback: NCCL
+            # send/recv into a local halo buffer each step.
             cap = -(-(stored - 2) // world) + 2
             try:
                 import torch.distributed._symmetric_memory as symm
@@ -241,7 +243,7 @@ class BlurWorkload(Workload):
                 if self.band.recvs_halo:
                     peer = hdl.get_buffer(rank + 1, (cap, n), torch.float32)
                     self.halo = peer[0:2]
-                self.transport = "peer loads over NVLink (symmetric memory)"
+                self.transport = "copy engine over NVLink from the neighbour's band (symmetric memory) into a local slot, inside the step"
                 self._symm = (buf, hdl)
                 # every band is complete before any rank's kernel may read a neighbour's rows
                 torch.cuda.synchronize()
@@ -871,7 +873,7 @@ def run_reference_arm(args, rank, world):
     shell = cls.__new__(cls)
     shell.world = world
     shell.mode = "single" if world == 1 else "weak"
-    shell.transport = "peer loads over NVLink (symmetric memory)"
+    shell.transport = "copy engine over NVLink from the neighbour's band (symmetric memory) into a local slot, inside the step"
     shell.band = type("B", (), {"band_rows": getattr(cls, "N", 0)})()
     shell.rows = getattr(cls, "ROWS", 0)
     shell.nq = getattr(cls, "NQ", 0)

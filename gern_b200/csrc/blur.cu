@@ -196,9 +196,12 @@ template <int ROWS>
 __global__ void __launch_bounds__(128)
 blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
                    float *__restrict__ out, int64_t out_ld, int out_rows, int out_vec,
-                   int in_rows_local, const float *__restrict__ halo, int64_t halo_ld) {
+                   int in_rows_local, const float *__restrict__ halo, int64_t halo_ld,
+                   const int *__restrict__ halo_flag, int halo_expect, int *status) {
     // Input rows >= in_rows_local are not in `in`: they are the rows of the next row band and
-    // are read from `halo` (which may be a peer GPU's memory; ordinary loads only).
+    // are read from `halo` (which may be a peer GPU's memory; ordinary loads only).  With
+    // `halo_flag`, `halo` is a local slot that a copy engine fills: the blocks that read it wait
+    // (bounded) until the flag holds `halo_expect`.
     const int out_cols = in_cols - 2;
     // one-dimensional grid (the y extent of a grid stops at 65535 block rows): column blocks
     // fastest, so that blocks in flight walk the image row-major
@@ -227,6 +230,7 @@ blur3x3_reg_kernel(const float *__restrict__ in, int64_t in_ld, int in_cols,
     const float *src = in + static_cast<int64_t>(r_begin) * in_ld + c0;
     float *dst = out + static_cast<int64_t>(r_begin) * out_ld + c0;
     const bool local = r_begin + n_out + 2 <= in_rows_local;   // uniform over the block
+    if (!local && halo_flag != nullptr) wait_flag_equals(halo_flag, halo_expect, status, 320);
     // the block row that needs the halo takes the same vector path when the halo rows are
     // 16-byte aligned: all its loads, the remote ones included, are in flight at once
     const bool halo_vec = halo != nullptr && (reinterpret_cast<uintptr_t>(halo) & 15) == 0 && halo_ld % 4 == 0;
@@ -439,6 +443,61 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
 }
 
 // `in_rows` counts the halo rows too: in holds in_rows - (halo ? 2 : 0) rows.
+// Halo rows on another device: a copy engine brings them into the next slot of the context's ring
+// and then sets the slot's flag, on a stream of its own, so that the blur kernel itself reads
+// local memory only.  (A grid that has read a peer's memory completes about 3 us later, measured,
+// whatever it read; the kernels of a stream of dependent launches would each pay that.)  On return
+// *slot_rows is the slot (NULL if `halo` is memory of this device, or not device memory the
+// driver knows: the kernel then reads it directly), *flag its flag and *expect the flag's value.
+static int halo_prefetch(gb200_ctx *ctx, const float *halo, int64_t halo_ld, int64_t in_cols,
+                         const float **slot_rows, const int **flag, int *expect) {
+    *slot_rows = nullptr;
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, halo) != cudaSuccess) {
+        cudaGetLastError();
+        return GB200_OK;
+    }
+    if (at.type != cudaMemoryTypeDevice || at.device == ctx->device) return GB200_OK;
+    if (ctx->halo_stream == nullptr) {
+        GB200_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->halo_stream, cudaStreamNonBlocking));
+        GB200_CUDA_TRY(cudaMalloc(&ctx->halo_flags, kHaloSlots * sizeof(int)));
+        GB200_CUDA_TRY(cudaMemset(ctx->halo_flags, 0, kHaloSlots * sizeof(int)));
+        GB200_CUDA_TRY(cudaMallocHost(&ctx->halo_flag_values, 256 * sizeof(int)));
+        for (int i = 0; i < 256; ++i) ctx->halo_flag_values[i] = i + 1;
+        for (int i = 0; i < 4; ++i) GB200_CUDA_TRY(cudaEventCreateWithFlags(&ctx->halo_ev[i], cudaEventDisableTiming));
+    }
+    const size_t need = 2 * (size_t)in_cols;
+    if (ctx->halo_slot_floats < need) {
+        GB200_CUDA_TRY(cudaDeviceSynchronize());   // nothing may still read the old ring
+        if (ctx->halo_ring) GB200_CUDA_TRY(cudaFree(ctx->halo_ring));
+        ctx->halo_ring = nullptr;
+        ctx->halo_slot_floats = 0;
+        GB200_CUDA_TRY(cudaMalloc(&ctx->halo_ring, kHaloSlots * need * sizeof(float)));
+        ctx->halo_slot_floats = need;
+    }
+    const unsigned long long k = ctx->halo_step;
+    const int slot = (int)(k % kHaloSlots);
+    // the launch that read this slot last (32 steps back) must be over before it is overwritten
+    if (k >= (unsigned long long)kHaloSlots && k % kHaloEventEvery == 0)
+        GB200_CUDA_TRY(cudaStreamWaitEvent(ctx->halo_stream, ctx->halo_ev[(k / kHaloEventEvery) % 4], 0));
+    float *dst = ctx->halo_ring + (size_t)slot * ctx->halo_slot_floats;
+    GB200_CUDA_TRY(cudaMemcpy2DAsync(dst, (size_t)in_cols * sizeof(float), halo, (size_t)halo_ld * sizeof(float),
+                                     (size_t)in_cols * sizeof(float), 2, cudaMemcpyDefault, ctx->halo_stream));
+    GB200_CUDA_TRY(cudaMemcpyAsync(ctx->halo_flags + slot, ctx->halo_flag_values + (k & 255), sizeof(int),
+                                   cudaMemcpyHostToDevice, ctx->halo_stream));
+    *slot_rows = dst;
+    *flag = ctx->halo_flags + slot;
+    *expect = (int)(k & 255) + 1;
+    return GB200_OK;
+}
+// After the launch that reads the slot handed out by halo_prefetch.
+static int halo_prefetch_launched(gb200_ctx *ctx, cudaStream_t stream) {
+    const unsigned long long k = ctx->halo_step++;
+    if (k % kHaloEventEvery == kHaloEventEvery - 1)
+        GB200_CUDA_TRY(cudaEventRecord(ctx->halo_ev[(k / kHaloEventEvery) % 4], stream));
+    return GB200_OK;
+}
+
 template <int ROWS>
 static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in_rows,
                       int64_t in_cols, float *out, int64_t out_ld, cudaStream_t stream,
@@ -447,10 +506,23 @@ static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
     const int64_t n_blocks = ((out_cols + 511) / 512) * ((out_rows + ROWS - 1) / ROWS);
     GB200_REQUIRE(n_blocks < (1ll << 31), GB200_ERR_UNSUPPORTED, "blur: more than 2^31 blocks");
     dim3 grid((unsigned)n_blocks);
+    const float *slot_rows = nullptr;
+    const int *flag = nullptr;
+    int expect = 0;
+    if (halo != nullptr) {
+        int rc = halo_prefetch(ctx, halo, halo_ld, in_cols, &slot_rows, &flag, &expect);
+        if (rc) return rc;
+        if (slot_rows != nullptr) {
+            halo = slot_rows;
+            halo_ld = in_cols;
+        }
+    }
     GB200_CUDA_TRY(launch_pdl(blur3x3_reg_kernel<ROWS>, grid, dim3(128), 0, stream, in, in_ld, (int)in_cols,
                               out, out_ld, (int)out_rows, (aligned16(out) && out_ld % 4 == 0) ? 1 : 0,
-                              (int)(halo ? in_rows - 2 : in_rows), halo, halo_ld));
-    return after_launch(ctx, "blur3x3_reg_kernel");
+                              (int)(halo ? in_rows - 2 : in_rows), halo, halo_ld, flag, expect, ctx->d_status));
+    int rc = after_launch(ctx, "blur3x3_reg_kernel");
+    if (rc == GB200_OK && slot_rows != nullptr) rc = halo_prefetch_launched(ctx, stream);
+    return rc;
 }
 
 static int check_blur_args(const float *in, int64_t in_ld, int64_t in_rows, int64_t in_cols,

@@ -91,6 +91,15 @@ struct gb200_ctx {
     // zero whenever no such kernel is running (the merging block puts its counter back)
     int *merge_counters = nullptr;
     size_t merge_counter_words = 0;
+    // Halo rows that live on another device are fetched by a copy engine on `halo_stream` into a
+    // ring of local slots; a flag per slot tells the kernel that its rows have landed.
+    cudaStream_t halo_stream = nullptr;
+    float *halo_ring = nullptr;
+    size_t halo_slot_floats = 0;
+    int *halo_flags = nullptr;        // device, kHaloSlots words
+    int *halo_flag_values = nullptr;  // pinned host, 256 words: [i] = i + 1
+    unsigned long long halo_step = 0;
+    cudaEvent_t halo_ev[4] = {nullptr, nullptr, nullptr, nullptr};
     cudaStream_t copy_stream[2] = {nullptr, nullptr};
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
 };
@@ -104,6 +113,8 @@ int get_tmap_2d(gb200_ctx *ctx, const void *ptr, CUtensorMapDataType dtype, int 
                 CUtensorMapSwizzle swizzle, CUtensorMap *out);
 
 constexpr size_t kTmapCacheEntries = 512;
+constexpr int kHaloSlots = 32;      // ring of prefetched halo rows
+constexpr int kHaloEventEvery = 8;  // a slot is reused once the launch 32 steps back has finished: one event per 8 launches
 constexpr int kMaxGridY = 65535;   // CUDA's limit on gridDim.y and gridDim.z
 
 // Sets the device for the calling thread, as every entry point must before touching CUDA.
@@ -251,6 +262,25 @@ __device__ __forceinline__ bool mbar_wait_ns(uint64_t *bar, uint32_t parity, int
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, int code) {
     return mbar_wait_ns(bar, parity, status, code, kWaitLimitNs);
+}
+// Bounded wait for a word in global memory that a copy engine (or another device) writes after
+// the data it announces.  Returns false (after writing `code` to *status) when the time ran out.
+__device__ __forceinline__ bool wait_flag_equals(const int *flag, int value, int *status, int code) {
+    auto look = [&]() {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        return v == value;
+    };
+    for (int i = 0; i < 1024; ++i)
+        if (look()) return true;
+    const unsigned long long t0 = global_timer_ns();
+    while (true) {
+        for (int i = 0; i < 32; ++i)
+            if (look()) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
+    if (status) atomicExch(status, code);
+    return false;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

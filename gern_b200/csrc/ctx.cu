@@ -249,6 +249,12 @@ int gb200_ctx_destroy(gb200_ctx *ctx) {
         if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->merge_counters) cudaFree(ctx->merge_counters);
+    if (ctx->halo_stream) cudaStreamDestroy(ctx->halo_stream);
+    if (ctx->halo_ring) cudaFree(ctx->halo_ring);
+    if (ctx->halo_flags) cudaFree(ctx->halo_flags);
+    if (ctx->halo_flag_values) cudaFreeHost(ctx->halo_flag_values);
+    for (int i = 0; i < 4; ++i)
+        if (ctx->halo_ev[i]) cudaEventDestroy(ctx->halo_ev[i]);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     delete ctx;
