@@ -159,3 +159,30 @@ def test_bad_shard_arguments(ctxs):
     a = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
     arr[0] = api.Shard(c.handle, a.data_ptr(), a.data_ptr(), 128, None, None, None)
     assert api.lib.gb200_gemm_bf16_sharded(arr, 1, 64, 64, 64, 64, 64) == -1   # B replica missing
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs the halo rows on a second GPU")
+def test_band_with_halo_rows_on_another_device_over_many_steps(ctxs, oracle):
+    """A halo pointer into another device's memory is not read by the kernel: a copy engine brings
+    the two rows into the next of 32 local slots and sets the slot's flag.  A hundred steps with
+    fresh halo rows each time walk the ring three times (slot reuse behind the event of the launch
+    32 steps back); every step's last output rows are compared bit for bit with the oracle, and a
+    second band size in between makes the ring grow."""
+    c0 = ctxs(0)
+    rng = np.random.default_rng(5)
+    for rows, cols, steps in ((64, 1024, 70), (48, 2048, 40), (64, 1024, 10)):
+        band = rng.random((rows, cols), dtype=np.float32)
+        x = torch.from_numpy(band).to("cuda:0")
+        out = torch.empty((rows, cols - 2), device="cuda:0")
+        halos = [rng.random((2, cols), dtype=np.float32) for _ in range(steps)]
+        remote = [torch.from_numpy(h).to("cuda:1") for h in halos]    # complete before any call
+        torch.cuda.synchronize("cuda:1")
+        outs = []
+        for s in range(steps):
+            c0.blur3x3_band(x, remote[s], out)
+            outs.append(out[-4:].clone())          # stream order: after this step's kernel
+        c0.sync()
+        for s in range(steps):
+            want = oracle.blur_xy(np.concatenate([band[-4:], halos[s]]))
+            assert np.array_equal(outs[s].cpu().numpy(), want), (rows, cols, s)
+        assert np.array_equal(out[:8].cpu().numpy(), oracle.blur_xy(band[:10]))
