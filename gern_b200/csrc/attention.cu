@@ -559,7 +559,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // ---- epilogue: O / l -> bf16 -> global, or the segment's partial result ----
         if (lane_group == 0 && lane == 0) ATTN_TRACE(18 + 3 * t, seg);
         // A pair shared with other CTAs (BALANCED): partial results lie per warp as
-        // [part][column][lane] (a warp's store or load of one column is one 128-byte line);
+        // [part][four columns][lane][4] (a warp's store or load of four columns is 512 contiguous bytes);
         // whichever sharer finds all the others counted in merges them with its own O, which is
         // still in TMEM.  The last segment of a run is usually that sharer (the others were first
         // segments of their CTAs): it looks at the count while its last P V is still running.
@@ -568,7 +568,7 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int group = (sg.pair * TILES + t) * 4 + lane_group;          // 32 rows of the pair
         int *counter = counters + group;
         auto ml_at = [&](int k) { return part_ml + 2 * ((static_cast<int64_t>(group) * max_parts + k) * 32 + lane); };
-        auto o_at = [&](int k) { return part_o + (static_cast<int64_t>(group) * max_parts + k) * (32 * D) + lane; };
+        auto o_at = [&](int k) { return part_o + (static_cast<int64_t>(group) * max_parts + k) * (32 * D) + lane * 4; };
         int seen = -1;
         if (shared && it.cursor >= it.end) {
             if (lane == 0) asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
@@ -617,7 +617,10 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     tmem_ld_32x32(t_o + c * 32 + 32, o[1]);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) dst[(c * 32 + i) * 32] = __uint_as_float(o[i >> 5][i & 31]);
+                    for (int i = 0; i < 64; i += 4)
+                        *reinterpret_cast<float4 *>(dst + (c * 32 + i) * 32) =
+                            make_float4(__uint_as_float(o[i >> 5][i & 31]), __uint_as_float(o[i >> 5][(i & 31) + 1]),
+                                        __uint_as_float(o[i >> 5][(i & 31) + 2]), __uint_as_float(o[i >> 5][(i & 31) + 3]));
                 }
                 // the warp's stores, then one release that counts it in
                 __syncwarp();
@@ -647,7 +650,13 @@ attention_bf16_kernel(const __grid_constant__ CUtensorMap tmap_q,
                     ml = __ldcg(reinterpret_cast<const float2 *>(ml_at(k)));
                     const float *src = o_at(k) + c * 32 * 32;
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __ldcg(src + i * 32);
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 f = __ldcg(reinterpret_cast<const float4 *>(src + i * 32));
+                        v[i] = f.x;
+                        v[i + 1] = f.y;
+                        v[i + 2] = f.z;
+                        v[i + 3] = f.w;
+                    }
                 };
                 uint32_t o[32];
                 auto add_up = [&](int step, const float(&v)[32], const float2 &ml) {

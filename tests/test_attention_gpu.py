@@ -240,9 +240,10 @@ def test_equal_runs_merged_inside_the_kernel(ctx, oracle, nq, nkv):
     for o in outs:
         diff = (o.float() - o1.float()).norm(dim=1) / o1.float().norm(dim=1)
         assert float(diff.max()) <= 1e-2
-    # the same sharer normally merges on every launch; if another one did, the sums differ in their last bit
+    # the same sharer normally merges on every launch; if another one did, the fp32 sums were taken
+    # in another order: a few bf16 roundings fall the other way
     a, b = outs[0].float(), outs[1].float()
-    assert bool(((a - b).abs() <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-30).all())
+    assert float(((a - b).norm(dim=1) / a.norm(dim=1)).max()) <= 2e-3
     idx = sorted({(i * 9973) % nq for i in range(96)} | {0, nq - 1})
     sel = torch.tensor(idx, device="cuda")
     oracle.set_threads(oracle.max_threads())
