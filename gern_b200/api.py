@@ -318,7 +318,8 @@ class Context:
     def attention_bf16(self, Q, K, V, O, scale, stream=None, variant=None, splits=None):
         """splits (test hook): 0 = the library's choice, 1 = whole Q tile pairs per thread block,
         n > 1 = that many K/V ranges and a combine pass, -1 = equal runs of (pair, K/V block) units
-        per thread block, merged inside the kernel."""
+        per thread block, merged inside the kernel, -9 = whole pairs through the same instantiation
+        as the equal runs."""
         nq, d = Q.shape
         nkv = K.shape[0]
         if splits is not None:

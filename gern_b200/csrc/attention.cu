@@ -20,6 +20,11 @@
 // running maximum has grown by more than 2^8, and at the end normalise and store O.  The first half of P_t (kv 0-63) is announced to the
 // MMA warp while the second half is still being computed, so that half of P_t V_j runs under the
 // softmax.  Every wait is bounded and reports through the status word.
+//
+// How the pairs of Q tiles and their K/V blocks are dealt out to CTAs is a separate matter (three
+// schedules, see the enum below): whole pairs, K/V ranges with a combine kernel when there are few
+// Q rows, and equal runs of (pair, K/V block) units when whole pairs would leave SMs idle in their
+// last round; all roles walk the same list of segments, and the barrier phases run on across it.
 #include <float.h>
 
 #include <type_traits>
@@ -759,10 +764,10 @@ int attention_pair_launch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void
 // Equal runs per CTA are chosen when the longest CTA's walk plus this allowance (in K/V blocks)
 // comes to at most this share of the whole-pair schedule's.
 #ifndef GB200_ATTN_BALANCED_GAIN_PCT
-#define GB200_ATTN_BALANCED_GAIN_PCT 97
+#define GB200_ATTN_BALANCED_GAIN_PCT 95
 #endif
 #ifndef GB200_ATTN_BALANCED_COST_BLOCKS
-#define GB200_ATTN_BALANCED_COST_BLOCKS 3
+#define GB200_ATTN_BALANCED_COST_BLOCKS 4
 #endif
 
 // kernel_choice: 0 = pick, 1 = one CTA per two Q tiles, 2 = CTA pairs with two Q tiles per CTA
@@ -807,14 +812,22 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
         } else if ((balanced_time + GB200_ATTN_BALANCED_COST_BLOCKS) * 100 <= whole_time * GB200_ATTN_BALANCED_GAIN_PCT) {
             // The last wave of whole pairs would leave SMs idle: equal runs.  Handing a pair over
             // inside a CTA and merging the shared pairs at the end (all CTAs at once, bound by the
-            // L2) cost about three K/V blocks' time: 128 pairs x 32 blocks on 148 SMs gain little
-            // (measured 68.6 against 69.7 us), 157 pairs x 32 blocks take 80 instead of 135 us and
-            // 128 pairs x 128 blocks 230 instead of 262 us.
+            // L2) cost nearly four K/V blocks' time: 128 pairs x 32 blocks on 148 SMs gain nothing
+            // worth a result that depends on which CTA merges (measured 67.6 against 67.9 us) and
+            // stay whole, 157 pairs x 32 blocks take 80 instead of 135 us and 128 pairs x 128
+            // blocks 226 instead of 262 us.
             splits = -1;
         }
     }
     if (splits > total_blocks) splits = total_blocks;
     if (splits == -1 && (int64_t)grid * total_blocks > (int64_t)1 << 30) splits = 1;
+    // Whole pairs picked by the library for 16 K/V blocks or more go through the segment-walking
+    // instantiation with runs of one pair: the same bits, and its block loop measures 2-3 % faster
+    // than the WHOLE instantiation's (67.9 against 70.0 us at 32768 x 4096, 133 against 138 us at
+    // 65536 x 4096; 22.4 against 22.0 us at 32768 x 1024, hence the threshold).
+    if ((splits == 1 || splits == 0) && kv_splits == 0 && total_blocks >= 16 &&
+        (int64_t)grid * total_blocks < ((int64_t)1 << 30))
+        splits = -9;
     if (splits == 1 || splits == 0) {
         rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<WHOLE>, SMEM_BYTES);
         if (rc) return rc;
@@ -824,18 +837,21 @@ int attention_dispatch(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K
                                   static_cast<float *>(nullptr), 0, static_cast<int *>(nullptr)));
         return after_launch(ctx, "attention_bf16_kernel");
     }
-    if (splits == -1) {
+    if (splits == -1 || splits == -9) {
         const int64_t units = (int64_t)grid * total_blocks;
-        const int per = (int)((units + sms - 1) / sms);
+        const int per = splits == -9 ? total_blocks : (int)((units + sms - 1) / sms);
         const unsigned ctas = (unsigned)((units + per - 1) / per);
         const int max_parts = (total_blocks + per - 1) / per + 1;
         const size_t rows = (size_t)grid * max_parts * (BM * TILES);
-        rc = workspace_reserve(ctx, rows * (D + 2) * sizeof(float));
-        if (rc) return rc;
-        rc = merge_counters_reserve(ctx, (size_t)grid * TILES * 4);
-        if (rc) return rc;
-        float *part_o = static_cast<float *>(ctx->workspace);
-        float *part_ml = part_o + rows * D;
+        float *part_o = nullptr, *part_ml = nullptr;
+        if (per != total_blocks) {      // runs of whole pairs share nothing
+            rc = workspace_reserve(ctx, rows * (D + 2) * sizeof(float));
+            if (rc) return rc;
+            rc = merge_counters_reserve(ctx, (size_t)grid * TILES * 4);
+            if (rc) return rc;
+            part_o = static_cast<float *>(ctx->workspace);
+            part_ml = part_o + rows * D;
+        }
         rc = ensure_dynamic_smem(ctx, attention_bf16_kernel<BALANCED>, SMEM_BYTES);
         if (rc) return rc;
         GB200_CUDA_TRY(launch_pdl(attention_bf16_kernel<BALANCED>, dim3(ctas), dim3(NUM_THREADS), (size_t)SMEM_BYTES,
@@ -936,14 +952,14 @@ int gb200_attention_bf16_variant(gb200_ctx *ctx, const void *Q, int64_t ldq, con
 
 // Test / benchmark hook: the single-CTA kernel with the schedule chosen by the caller (0 = let the
 // library pick, 1 = whole pairs, n > 1 = that many K/V ranges and a combine pass, -1 = equal runs
-// per CTA merged inside the kernel).
+// per CTA merged inside the kernel, -9 = whole pairs through the segment-walking instantiation).
 int gb200_attention_bf16_splitkv(gb200_ctx *ctx, const void *Q, int64_t ldq, const void *K, int64_t ldk,
                                  const void *V, int64_t ldv, void *O, int64_t ldo, int64_t nq,
                                  int64_t nkv, int64_t d, float scale, void *stream, int splits) {
     DeviceScope scope;
     int rc = scope.enter(ctx);
     if (rc) return rc;
-    GB200_REQUIRE(splits >= -1 && splits <= 1024, GB200_ERR_INVALID_ARG, "splits out of range");
+    GB200_REQUIRE((splits >= -1 || splits == -9) && splits <= 1024, GB200_ERR_INVALID_ARG, "splits out of range");
     rc = check_attention_args(Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale);
     if (rc) return rc < 0 ? rc : GB200_OK;
     return attention_dispatch(ctx, Q, ldq, K, ldk, V, ldv, O, ldo, nq, nkv, d, scale,

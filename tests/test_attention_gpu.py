@@ -252,6 +252,21 @@ def test_equal_runs_merged_inside_the_kernel(ctx, oracle, nq, nkv):
     assert frob(outs[1][sel].float().cpu().numpy(), want) <= 1e-2
 
 
+@pytest.mark.parametrize("nq,nkv", [(5000, 3000), (300, 128), (38000, 2048)])
+def test_runs_of_whole_pairs_give_the_bits_of_the_whole_pair_kernel(ctx, nq, nkv):
+    """splits = -9: the segment-walking instantiation with runs of exactly one pair (what the library
+    picks for whole pairs from 16 K/V blocks up): nothing is shared, so the bits are those of the
+    plain whole-pair kernel (splits = 1)."""
+    q, k, v = make(nq, nkv, nq + 7 * nkv)
+    outs = []
+    for splits in (1, -9):
+        o = torch.zeros((nq, 128), dtype=torch.bfloat16, device="cuda")
+        ctx.attention_bf16(q, k, v, o, 0.11, splits=splits)
+        outs.append(o)
+    ctx.sync()
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_equal_runs_after_a_different_shape_and_with_a_padded_pitch(ctx, oracle):
     """The counters and the partial-result workspace are shared by all launches of a context."""
     scale = 0.1
