@@ -896,7 +896,13 @@ static int check_attention_args(const void *Q, int64_t ldq, const void *K, int64
     return GB200_OK;
 }
 
-int kernel_regs_attention() { return kernel_registers(attention_bf16_kernel<WHOLE>); }
+// Registers per thread of the widest instantiation (the library picks among them per shape).
+int kernel_regs_attention() {
+    const int a = kernel_registers(attention_bf16_kernel<WHOLE>), b = kernel_registers(attention_bf16_kernel<SPLIT>),
+              c = kernel_registers(attention_bf16_kernel<BALANCED>);
+    if (a < 0 || b < 0 || c < 0) return -1;
+    return a > b ? (a > c ? a : c) : (b > c ? b : c);
+}
 
 }  // namespace gb200
 
