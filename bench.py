@@ -716,7 +716,7 @@ class GemmF32Workload(Workload):
     unit = "TFLOP/s"
     dtype = "f32"
     bound = "tensor"
-    kernel = "gemm_f32_warpk_kernel"
+    kernel = "gemm_f32_fused_kernel"
     sharded = False
     N = 512
 

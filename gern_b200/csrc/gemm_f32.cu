@@ -202,29 +202,40 @@ int gemm_f32_tc_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const floa
 #endif
 
 int gemm_f32_fused_launch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,
-                          int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate, cudaStream_t stream);
+                          int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate, cudaStream_t stream,
+                          int cluster_hint = 0);
 
-// The single-launch tensor-core kernel (gemm_f32_fused.cu) is selectable but never picked: from cold
-// L2 it measured 22 / 33 / 45 / 57 us at 256^3 / 512^3 / 768^3 / 1024^3 against 11 / 21 / 47 / 110 us
-// for the CUDA-core kernels and 22 / 30 / 40 / 47 us for the three-launch tensor-core path, so one of
-// the other two is faster at every size (its eight converting warps are bound by the fp32 -> bf16
-// conversions, three per operand element, not by the MMAs).
+// The single-launch tensor-core kernel (gemm_f32_fused.cu) takes the middle: from cold L2 it measures
+// 14.8 / 21.2 / 22.7 / 40.0 us at 512^3 / 640^3 / 768^3 / 1024^3 against 21.6 / 33.0 / 47.6 / 110 us
+// for the CUDA-core kernels, 30 / 34 / 41 / 48 us for the three-launch tensor-core path and 20.1 /
+// 25.1 / 28.0 / 51.2 us for cuBLAS with tf32 off; at 256^3 / 384^3 the CUDA-core kernel is faster
+// (12.1 / 13.9 against 14.6 / 16.5 us), and from about 3 GFLOP (more than one round of its 128 x 64
+// tiles, whose eight converting warps are bound by the fp32 -> bf16 conversions) the pre-passes pay.
 #ifndef GB200_GEMM_F32_FUSED_MIN_FLOP
-#define GB200_GEMM_F32_FUSED_MIN_FLOP 1.0e30
+#define GB200_GEMM_F32_FUSED_MIN_FLOP 2.0e8
+#endif
+#ifndef GB200_GEMM_F32_FUSED_MAX_FLOP
+#define GB200_GEMM_F32_FUSED_MAX_FLOP 3.0e9
 #endif
 
 // kernel_choice: 0 = pick, 1 = CUDA cores, 2 = tensor cores with split pre-passes (three launches),
-// 3 = tensor cores with the split inside the kernel (one launch).
+// 3 = tensor cores with the split inside the kernel (one launch; a cluster per tile shares its K
+// range when there are few tiles), 5 = the same without clusters.
 int gemm_f32_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb,
                       float *C, int64_t ldc, int64_t M, int64_t N, int64_t K, int accumulate,
                       cudaStream_t stream, int kernel_choice = 0) {
     const bool tc_ok = ctx->encode_tiled != nullptr && K > 0;
     const double flop = 2.0 * (double)M * (double)N * (double)K;
     const bool tc_pays = flop >= GB200_GEMM_F32_TC_MIN_FLOP;
-    if (tc_ok && (kernel_choice == 2 || (kernel_choice == 0 && tc_pays)))
+    // one round of 128 x 64 tiles at most, and not so few K chunks that the prologue dominates
+    const int64_t fused_tiles = ((M + 127) / 128) * ((N + 63) / 64);
+    const bool fused_pays = tc_ok && flop >= GB200_GEMM_F32_FUSED_MIN_FLOP && flop < GB200_GEMM_F32_FUSED_MAX_FLOP &&
+                            fused_tiles <= ctx->sm_count && K >= 256;
+    if (tc_ok && (kernel_choice == 2 || (kernel_choice == 0 && tc_pays && !fused_pays)))
         return gemm_f32_tc_dispatch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream);
-    if (K > 0 && (kernel_choice == 3 || (kernel_choice == 0 && flop >= GB200_GEMM_F32_FUSED_MIN_FLOP)))
-        return gemm_f32_fused_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream);
+    if (K > 0 && (kernel_choice == 3 || kernel_choice == 5 || (kernel_choice == 0 && fused_pays)))
+        return gemm_f32_fused_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, accumulate, stream,
+                                     kernel_choice == 5 ? 1 : 0);
     const int64_t big_tiles = ((M + 127) / 128) * ((N + 127) / 128);
     const bool big = big_tiles >= 2 * (int64_t)ctx->sm_count;
     const int bm = big ? 128 : 32;

@@ -62,12 +62,13 @@ def test_f32_shapes(ctx, oracle, mnk):
     assert frob(cg.cpu().numpy(), want - c0) < 1e-5
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 5])
 @pytest.mark.parametrize("mnk", [(1, 1, 1), (5, 7, 3), (64, 64, 64), (100, 130, 250), (257, 129, 513), (512, 512, 512),
-                                 (1024, 768, 300)])
+                                 (1024, 768, 300), (256, 256, 256), (130, 70, 1100)])
 def test_f32_kernel_variants(ctx, oracle, mnk, variant):
     """CUDA-core kernels (1), the tensor-core path with three-way bf16 splits in pre-passes (2) and
-    the single-launch kernel that splits in shared memory (3), forced: all must meet the fp32 bars (|delta| < 1e-3, relative Frobenius error < 1e-5), with and
+    the single-launch kernel that splits in shared memory (3: with a cluster per tile sharing the K
+    range when there are few tiles; 5: without clusters), forced: all must meet the fp32 bars (|delta| < 1e-3, relative Frobenius error < 1e-5), with and
     without accumulation into C."""
     m, n, k = mnk
     rng = np.random.default_rng(m * 77 + n * 3 + k)
@@ -99,7 +100,7 @@ def test_f32_tensor_core_path_is_exact_on_small_integers(ctx):
     a = (torch.arange(m * k, device="cuda") % 13).float().reshape(m, k)
     b = (torch.arange(k * n, device="cuda") % 7).float().reshape(k, n)
     c = torch.zeros((m, n), device="cuda")
-    for variant in (2, 3):
+    for variant in (2, 3, 5):
         c.zero_()
         ctx.gemm_f32(a, b, c, variant=variant)
         ctx.sync()
