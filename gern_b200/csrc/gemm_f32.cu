@@ -198,7 +198,7 @@ int gemm_f32_tc_dispatch(gb200_ctx *ctx, const float *A, int64_t lda, const floa
                          cudaStream_t stream);
 
 #ifndef GB200_GEMM_F32_TC_MIN_FLOP
-#define GB200_GEMM_F32_TC_MIN_FLOP 6.0e8   // measured: 512^3 19.0 vs 24.8 us, 768^3 43.6 vs 34.7 us
+#define GB200_GEMM_F32_TC_MIN_FLOP 6.0e8   // pre-pass path against the CUDA cores: 512^3 19.0 vs 24.8 us, 768^3 43.6 vs 34.7 us
 #endif
 
 int gemm_f32_fused_launch(gb200_ctx *ctx, const float *A, int64_t lda, const float *B, int64_t ldb, float *C,

@@ -89,8 +89,9 @@ int gb200_kernel_resources_query(const char *kernel, gb200_kernel_resources *out
 
 /* fp32 C (+)= A * B, all row-major.  A: M x K (lda), B: K x N (ldb), C: M x N (ldc).
  * accumulate != 0 adds into C (Gern's leaf does `c += sum`), 0 overwrites C.  Problems above
- * 0.6 GFLOP run on the tensor cores with every fp32 operand split into three bf16 terms (fp32
- * accuracy is kept; the library's workspace holds the split copies), smaller ones on CUDA cores.
+ * 0.2 GFLOP run on the tensor cores with every fp32 operand split into three bf16 terms (fp32
+ * accuracy is kept): up to 3 GFLOP in one launch that splits in shared memory, beyond that with
+ * split pre-passes (the library's workspace holds the split copies); smaller ones on CUDA cores.
  * Replaces the emitted kernel of gernels/mm/kernel_10.cu:108-131 (copy:
  * gernels/mm/bench.cu:10-44) and its leaf `matrix_multiply<k_dim>`
  * (gernels/mm/impl/matrix_multiply.h:50-61); CPU twin gern::impl::matrix_multiply
