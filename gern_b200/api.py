@@ -64,6 +64,8 @@ lib.gb200_last_error_string.restype = ctypes.c_char_p
 lib.gb200_version.restype = ctypes.c_char_p
 lib.gb200_selftest_bounded_wait.argtypes = [_vp, ctypes.c_ulonglong, _vp, _vp]
 lib.gb200_selftest_bounded_wait.restype = _int
+lib.gb200_selftest_bounded_flag_wait.argtypes = [_vp, ctypes.c_ulonglong, _vp, _vp]
+lib.gb200_selftest_bounded_flag_wait.restype = _int
 lib.gb200_launch_count.argtypes = [_vp]
 lib.gb200_launch_count.restype = _i64
 lib.gb200_gemm_bf16_splitk_static.argtypes = [_vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _i64, _int, _vp]

@@ -285,7 +285,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *s
 }
 // Bounded wait for a word in global memory that a copy engine (or another device) writes after
 // the data it announces.  Returns false (after writing `code` to *status) when the time ran out.
-__device__ __forceinline__ bool wait_flag_equals(const int *flag, int value, int *status, int code) {
+__device__ __forceinline__ bool wait_flag_equals_ns(const int *flag, int value, int *status, int code,
+                                                    unsigned long long limit_ns) {
     auto look = [&]() {
         int v;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
@@ -297,10 +298,13 @@ __device__ __forceinline__ bool wait_flag_equals(const int *flag, int value, int
     while (true) {
         for (int i = 0; i < 32; ++i)
             if (look()) return true;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        if (global_timer_ns() - t0 > limit_ns) break;
     }
     if (status) atomicExch(status, code);
     return false;
+}
+__device__ __forceinline__ bool wait_flag_equals(const int *flag, int value, int *status, int code) {
+    return wait_flag_equals_ns(flag, value, status, code, kWaitLimitNs);
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -159,11 +159,35 @@ __global__ void bounded_wait_probe_kernel(int *status, unsigned long long limit_
     }
 }
 
+// The same for the one wait on a word in global memory (the blur's halo block row waiting for its
+// slot's flag): the probe waits for a value nobody writes; code 902.
+__global__ void bounded_flag_wait_probe_kernel(int *status, unsigned long long limit_ns, int *returned,
+                                               const int *flag) {
+    if (threadIdx.x == 0) {
+        const bool seen = wait_flag_equals_ns(flag, 0x7fffffff, status, 902, limit_ns);
+        *returned = seen ? 2 : 1;
+    }
+}
+
 }  // namespace gb200
 
 using namespace gb200;
 
 extern "C" {
+
+// Test hook: the flag-wait probe; `returned` doubles as the flag (the probe never sees 0x7fffffff in it
+// before it gives up and overwrites it).
+int gb200_selftest_bounded_flag_wait(gb200_ctx *ctx, unsigned long long limit_ns, int *returned, void *stream) {
+    DeviceScope scope;
+    int rc = scope.enter(ctx);
+    if (rc) return rc;
+    GB200_REQUIRE(returned != nullptr, GB200_ERR_INVALID_ARG, "returned is NULL");
+    GB200_REQUIRE(limit_ns <= 100ull * 1000ull * 1000ull, GB200_ERR_INVALID_ARG,
+                  "the probe's limit is capped at 100 ms");
+    bounded_flag_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ctx->d_status, limit_ns, returned,
+                                                                                  returned);
+    return after_launch(ctx, "bounded_flag_wait_probe_kernel");
+}
 
 // Test hook (not part of the documented surface): launches the probe above on `stream`.
 // `returned` is a device int that the kernel sets to 1 when the wait gave up (2 if it completed).

@@ -41,3 +41,17 @@ def test_a_host_entry_point_reports_the_timeout_itself(ctx):
     assert e.value.code == -5
     ctx.blur3x3_host(x, out)                    # reported once; the next call is clean
     assert (out == 1.0).all()
+
+
+def test_a_flag_wait_that_runs_out_is_reported_too(ctx):
+    """The one wait on a word in global memory (the blur's halo block row waits for the flag its
+    context's copy stream sets): a probe waits 2 ms for a value nobody writes."""
+    from gern_b200 import api
+    ctx.sync()
+    returned = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert api.lib.gb200_selftest_bounded_flag_wait(ctx.handle, 2_000_000, returned.data_ptr(), None) == 0
+    with pytest.raises(api.GernB200Error) as e:
+        ctx.sync()
+    assert e.value.code == -5 and "status code 902" in str(e.value)
+    assert int(returned.item()) == 1
+    ctx.sync()
