@@ -447,17 +447,37 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
 // and then sets the slot's flag, on a stream of its own, so that the blur kernel itself reads
 // local memory only.  (A grid that has read a peer's memory completes about 3 us later, measured,
 // whatever it read; the kernels of a stream of dependent launches would each pay that.)  On return
-// *slot_rows is the slot (NULL if `halo` is memory of this device, or not device memory the
-// driver knows: the kernel then reads it directly), *flag its flag and *expect the flag's value.
+// *slot_rows is the slot, *flag its flag and *expect the flag's value.
+// The device that owns `p` if it is another device's memory, else -1 (this device's memory, or
+// memory the driver does not know as device memory).
+static int other_device_of(gb200_ctx *ctx, const void *p) {
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return (at.type == cudaMemoryTypeDevice && at.device != ctx->device) ? at.device : -1;
+}
+// Whether kernels of the context's device may read device `dev`'s memory (peer access is switched
+// on at the first question; memory mapped with its own access rights, such as symmetric memory,
+// needs no more than that).
+static bool peer_readable(gb200_ctx *ctx, int dev) {
+    if (dev < 0 || dev >= 64) return false;
+    if (ctx->peer_state[dev] == 0) {
+        int can = 0;
+        if (cudaDeviceCanAccessPeer(&can, ctx->device, dev) != cudaSuccess) cudaGetLastError();
+        if (can) {
+            const cudaError_t e = cudaDeviceEnablePeerAccess(dev, 0);
+            if (e != cudaSuccess) cudaGetLastError();
+            can = (e == cudaSuccess || e == cudaErrorPeerAccessAlreadyEnabled);
+        }
+        ctx->peer_state[dev] = can ? 1 : -1;
+    }
+    return ctx->peer_state[dev] == 1;
+}
 static int halo_prefetch(gb200_ctx *ctx, const float *halo, int64_t halo_ld, int64_t in_cols,
                          const float **slot_rows, const int **flag, int *expect) {
     *slot_rows = nullptr;
-    cudaPointerAttributes at;
-    if (cudaPointerGetAttributes(&at, halo) != cudaSuccess) {
-        cudaGetLastError();
-        return GB200_OK;
-    }
-    if (at.type != cudaMemoryTypeDevice || at.device == ctx->device) return GB200_OK;
     if (ctx->halo_stream == nullptr) {
         GB200_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->halo_stream, cudaStreamNonBlocking));
         GB200_CUDA_TRY(cudaMalloc(&ctx->halo_flags, kHaloSlots * sizeof(int)));
@@ -509,10 +529,14 @@ static int launch_reg(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
     const float *slot_rows = nullptr;
     const int *flag = nullptr;
     int expect = 0;
-    if (halo != nullptr) {
-        int rc = halo_prefetch(ctx, halo, halo_ld, in_cols, &slot_rows, &flag, &expect);
-        if (rc) return rc;
-        if (slot_rows != nullptr) {
+    const int halo_dev = halo != nullptr ? other_device_of(ctx, halo) : -1;
+    if (halo_dev >= 0) {
+        // Large bands: the copy engine (the copy hides under the kernel).  Small ones read the rows
+        // themselves, unless this device's kernels cannot read that device's memory at all.
+        const bool large = in_rows * in_cols * (int64_t)sizeof(float) >= ctx->halo_prefetch_min_bytes;
+        if (large || !peer_readable(ctx, halo_dev)) {
+            int rc = halo_prefetch(ctx, halo, halo_ld, in_cols, &slot_rows, &flag, &expect);
+            if (rc) return rc;
             halo = slot_rows;
             halo_ld = in_cols;
         }
@@ -607,6 +631,13 @@ int gb200_blur3x3_f32_variant(gb200_ctx *ctx, const float *in, int64_t in_ld, in
                          static_cast<cudaStream_t>(stream), variant);
 }
 
+// Test hook: the band size from which a halo on another device is prefetched by a copy engine.
+int gb200_ctx_set_halo_prefetch_min_bytes(gb200_ctx *ctx, long long bytes) {
+    GB200_REQUIRE(ctx != nullptr && bytes >= 0, GB200_ERR_INVALID_ARG, "bad argument");
+    ctx->halo_prefetch_min_bytes = bytes;
+    return GB200_OK;
+}
+
 int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t band_rows,
                            int64_t in_cols, const float *halo, int64_t halo_ld, float *out,
                            int64_t out_ld, void *stream_) {
@@ -624,6 +655,10 @@ int gb200_blur3x3_f32_band(gb200_ctx *ctx, const float *in, int64_t in_ld, int64
     if (aligned16(in) && in_ld % 4 == 0)
         return launch_reg<4>(ctx, in, in_ld, band_rows + 2, in_cols, out, out_ld, stream, halo,
                              halo_ld);
+    const int halo_dev = other_device_of(ctx, halo);
+    GB200_REQUIRE(halo_dev < 0 || peer_readable(ctx, halo_dev), GB200_ERR_UNSUPPORTED,
+                  "the halo rows are on device %d, which device %d cannot read, and an unaligned band has no "
+                  "copy-engine path", halo_dev, ctx->device);
     return launch_direct(ctx, in, in_ld, band_rows, halo, halo_ld, in_cols, out, out_ld, 0,
                          band_rows, stream);
 }

@@ -99,6 +99,11 @@ struct gb200_ctx {
     int *halo_flags = nullptr;        // device, kHaloSlots words
     int *halo_flag_values = nullptr;  // pinned host, 256 words: [i] = i + 1
     unsigned long long halo_step = 0;
+    // Bands below this many input bytes read a remote halo themselves: the two copy operations of a
+    // step take 7-8 us on the copy stream, which a kernel shorter than that would wait for
+    // (8192-column bands at N = 8, 1024 rows: 17.2 us per step prefetched, 12.5 us read directly).
+    long long halo_prefetch_min_bytes = 48ll << 20;
+    signed char peer_state[64] = {0};   // per device: 0 not asked, 1 this device's kernels may read it, -1 they may not
     cudaEvent_t halo_ev[4] = {nullptr, nullptr, nullptr, nullptr};
     cudaStream_t copy_stream[2] = {nullptr, nullptr};
     cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};

@@ -190,8 +190,8 @@ int gb200_blur3x3_f32(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
  * rows of the band this GPU owns and `halo` holds the 2 rows that follow it (they belong to
  * the next band; `halo` may point into a peer GPU's memory, it is read with ordinary loads).
  * Produces band_rows output rows.  With halo == NULL it produces band_rows-2 rows (last band).
- * When `halo` is memory of another device (and the image is 16-byte aligned), the two rows are
- * not read by the kernel: a copy engine fetches them on a stream of the context into a local slot
+ * When `halo` is memory of another device (and the image is 16-byte aligned and the band holds at
+ * least 48 MiB), the two rows are not read by the kernel: a copy engine fetches them on a stream of the context into a local slot
  * as soon as the call is made, and the block row that needs them waits for the slot's flag.  The
  * neighbour's two rows must therefore be complete when the call is made, not merely earlier in
  * `stream`'s order, and such a call cannot be captured into a CUDA graph.

@@ -3,6 +3,8 @@
 With one GPU the shards are placed on the same device through separate contexts, which runs the
 whole host path (argument checks, per-shard launches, halo pointers into the next band); with two
 or more GPUs the same tests place one shard per device, and the blur halo is a peer load."""
+import ctypes
+
 import numpy as np
 import pytest
 import torch
@@ -168,7 +170,10 @@ def test_band_with_halo_rows_on_another_device_over_many_steps(ctxs, oracle):
     fresh halo rows each time walk the ring three times (slot reuse behind the event of the launch
     32 steps back); every step's last output rows are compared bit for bit with the oracle, and a
     second band size in between makes the ring grow."""
+    from gern_b200 import api
     c0 = ctxs(0)
+    # small bands read a remote halo directly by default: make this context prefetch at any size
+    assert api.lib.gb200_ctx_set_halo_prefetch_min_bytes(c0.handle, ctypes.c_longlong(0)) == 0
     rng = np.random.default_rng(5)
     for rows, cols, steps in ((64, 1024, 70), (48, 2048, 40), (64, 1024, 10)):
         band = rng.random((rows, cols), dtype=np.float32)
@@ -186,3 +191,8 @@ def test_band_with_halo_rows_on_another_device_over_many_steps(ctxs, oracle):
             want = oracle.blur_xy(np.concatenate([band[-4:], halos[s]]))
             assert np.array_equal(outs[s].cpu().numpy(), want), (rows, cols, s)
         assert np.array_equal(out[:8].cpu().numpy(), oracle.blur_xy(band[:10]))
+    # and the same band with the default threshold: the kernel reads the other device's rows itself
+    assert api.lib.gb200_ctx_set_halo_prefetch_min_bytes(c0.handle, ctypes.c_longlong(48 << 20)) == 0
+    c0.blur3x3_band(x, remote[-1], out)
+    c0.sync()
+    assert np.array_equal(out[-4:].cpu().numpy(), oracle.blur_xy(np.concatenate([band[-4:], halos[-1]])))
