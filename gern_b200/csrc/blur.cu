@@ -451,12 +451,16 @@ static int launch_tma(gb200_ctx *ctx, const float *in, int64_t in_ld, int64_t in
 // The device that owns `p` if it is another device's memory, else -1 (this device's memory, or
 // memory the driver does not know as device memory).
 static int other_device_of(gb200_ctx *ctx, const void *p) {
+    if (p == ctx->last_halo) return ctx->last_halo_device;   // a loop of steps asks about the same rows
     cudaPointerAttributes at;
-    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    int dev = -1;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess)
         cudaGetLastError();
-        return -1;
-    }
-    return (at.type == cudaMemoryTypeDevice && at.device != ctx->device) ? at.device : -1;
+    else if (at.type == cudaMemoryTypeDevice && at.device != ctx->device)
+        dev = at.device;
+    ctx->last_halo = p;
+    ctx->last_halo_device = dev;
+    return dev;
 }
 // Whether kernels of the context's device may read device `dev`'s memory (peer access is switched
 // on at the first question; memory mapped with its own access rights, such as symmetric memory,

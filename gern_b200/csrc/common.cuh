@@ -103,6 +103,8 @@ struct gb200_ctx {
     // step take 7-8 us on the copy stream, which a kernel shorter than that would wait for
     // (8192-column bands at N = 8, 1024 rows: 17.2 us per step prefetched, 12.5 us read directly).
     long long halo_prefetch_min_bytes = 48ll << 20;
+    const void *last_halo = nullptr;    // the halo pointer of the last band call and the device that owns it
+    int last_halo_device = -1;
     signed char peer_state[64] = {0};   // per device: 0 not asked, 1 this device's kernels may read it, -1 they may not
     cudaEvent_t halo_ev[4] = {nullptr, nullptr, nullptr, nullptr};
     cudaStream_t copy_stream[2] = {nullptr, nullptr};
