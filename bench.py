@@ -1013,11 +1013,16 @@ def main():
         if pre is None and getattr(wl, "graph_ok", False):
             # the K timed launches as one graph (see BlurWorkload): every call under capture is one
             # the warm-up has already made, so nothing but kernel launches is recorded
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                for i in range(steps):
-                    wl.step(torch.cuda.current_stream())
-            wl.timed_as = "one CUDA graph of the K launches"
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    for i in range(steps):
+                        wl.step(torch.cuda.current_stream())
+                wl.timed_as = "one CUDA graph of the K launches"
+            except Exception as e:  # noqa: BLE001  (fall back to launching one by one)
+                graph = None
+                torch.cuda.synchronize()
+                wl.timed_as = f"K launches back to back (graph capture failed: {type(e).__name__})"
         sync()
         l0 = ctx.launch_count()
         start.record()
