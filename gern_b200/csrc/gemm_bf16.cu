@@ -412,7 +412,8 @@ int pick_splits(int64_t n_tiles, int64_t k_blocks, int sm_count) {
 }
 
 int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
-                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream);
+                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream,
+                          int tile_n_hint = 0);
 
 // Tile width for the single-CTA kernel: rounds of tiles over the SMs times the time of one tile
 // (tensor-bound at 256 and 192 columns, shared-memory-bound and a little slower per flop at 128).
@@ -505,8 +506,8 @@ int gemm_f32x3_launch(gb200_ctx *ctx, const void *A3, const void *B3, float *C, 
     return launch_tc_f32x3<256>(ctx, A3, B3, C, ldc, M, N, Kp, accumulate, stream);
 }
 
-// kernel_choice: 0 = pick, 1 = single-CTA 128 x 256 tiles, 2 = CTA-pair tiles, 3 / 4 = single-CTA
-// tiles of 192 / 128 columns.
+// kernel_choice: 0 = pick, 1 = single-CTA 128 x 256 tiles, 2 = CTA-pair tiles (width picked), 3 / 4 =
+// single-CTA tiles of 192 / 128 columns, 5 / 6 = CTA-pair tiles of 224 / 256 columns.
 int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
                        void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream,
                        int forced_splits = 0, int kernel_choice = 0) {
@@ -539,10 +540,11 @@ int gemm_bf16_dispatch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B
     const int splits = forced_splits > 0 ? forced_splits : pick_splits(n_tiles, (K + BK - 1) / BK, ctx->sm_count);
     // CTA-pair tiles (256 x 256) when there are enough of them to fill the SM pairs
     const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    const bool want_pair = kernel_choice == 2 ||
+    const bool want_pair = kernel_choice == 2 || kernel_choice == 5 || kernel_choice == 6 ||
                            (kernel_choice == 0 && GB200_GEMM_AUTO_PAIR && pair_tiles >= ctx->sm_count / 2);
     if (want_pair && splits == 1 && forced_splits <= 1)
-        return gemm_bf16_2cta_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, stream);
+        return gemm_bf16_2cta_launch(ctx, A, lda, B, ldb, C, ldc, M, N, K, stream,
+                                     kernel_choice == 5 ? 224 : kernel_choice == 6 ? 256 : 0);
     if (splits == 1 && forced_splits <= 1 && kernel_choice != 1) {
         const int tile_n = kernel_choice == 3 ? 192 : kernel_choice == 4 ? 128
                                                                         : pick_tile_n(M, N, ctx->sm_count);

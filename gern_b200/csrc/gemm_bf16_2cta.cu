@@ -65,7 +65,10 @@ struct Gemm2F32 {
 };
 
 // MODE 0: bf16 C = A B.  MODE 1: fp32 C from three-way bf16 splits.  MODE 2: bf16 C with consumers.
-template <int MODE>
+// TN: columns of C per tile, 256 or 224 (each CTA then holds 112 rows of B in its 16 KiB slot; the
+// accumulator buffers stay 256 TMEM columns apart).  148 tiles of 224 columns are exactly two
+// rounds on 74 CTA pairs where 128 tiles of 256 columns are 1.73: see pick_pair_tile_n.
+template <int MODE, int TN = 256>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::NUM_THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16 *__restrict__ C,
@@ -86,7 +89,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    static_assert(TN % 32 == 0 && TN <= BN && (TN / 2) * BK * 2 <= B_BYTES, "tile width");
+    constexpr int B_HALF = TN / 2;                          // rows of B per CTA
+    constexpr int B_TILE_BYTES = B_HALF * BK * 2;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + TN - 1) / TN;
     const int n_tiles = tiles_m * tiles_n;
     const int k_blocks = (K + BK - 1) / BK;
 
@@ -130,7 +136,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (!mbar_wait(&empty[s], ph ^ 1, status, 221)) { ok = false; break; }
                     unsigned char *sa = smem + s * STAGE_BYTES;
                     // the leader's barrier collects the bytes of all four loads of the pair
-                    if (leader) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                    if (leader) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_TILE_BYTES));
                     const uint32_t full_leader = map_to_cta(smem_u32(&full[s]), 0);
                     int xa = kb * BK, xb = kb * BK;
                     if (F32X3) {
@@ -143,14 +149,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         xb = (seg_b * f32.seg_kb + r) * BK;
                     }
                     tma_load_2d_pair(sa, &tmap_a, xa, tm * BM + (int)rank * HALF, full_leader);
-                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, xb, tn * BN + (int)rank * HALF, full_leader);
+                    tma_load_2d_pair(sa + A_BYTES, &tmap_b, xb, tn * TN + (int)rank * B_HALF, full_leader);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
         if (leader && lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0);
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, TN, 0);
             uint32_t it = 0, tile_it = 0;
             bool ok = true;
             for (int t = pair; t < n_tiles && ok; t += n_pairs, ++tile_it) {
@@ -199,11 +205,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 if (f32.row_div) e_inv = 1.0f / f32.row_div[row];
             }
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
+            for (int ch = 0; ch < TN / 32; ++ch) {
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + ch * 32, r);
                 tmem_ld_wait();
-                const int col = tn * BN + ch * 32;
+                const int col = tn * TN + ch * 32;
                 if (EPI) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -293,23 +299,42 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
+// Tile width of the pair kernel: rounds of tiles over the CTA pairs times the width of a tile; 224
+// columns only where that is at least 5 % less than with 256.  1024 x 8192 (an eighth of 8192^2):
+// 128 tiles of 256 columns are two rounds of which the second is 0.73 full, 148 tiles of 224 are two
+// full ones.  Measured, the narrower MMAs do not run 224/256 as long, so the gain is 3 %, not 12:
+// 1024 x 8192 x 8192 90.1-92.7 against 93.8-94.6 us, 2048 x 8192 x 8192 177-178 against 184 us; where
+// the rounds come out equal (8192^3, 4096 x 8192 x 8192) 224 columns lose 4-15 % and are not picked.
+static int pick_pair_tile_n(int64_t M, int64_t N, int sm_count) {
+    const int64_t pairs = sm_count / 2 > 0 ? sm_count / 2 : 1;
+    auto cost = [&](int w) {
+        const int64_t tiles = ((M + gemm2::BM - 1) / gemm2::BM) * ((N + w - 1) / w);
+        return ((tiles + pairs - 1) / pairs) * w;
+    };
+    return cost(224) * 100 <= cost(256) * 95 ? 224 : 256;
+}
+
 // Launches the pair kernel; the caller has checked alignment (same rules as the single-CTA path).
+// tile_n_hint: 0 = pick the tile width, 224 / 256 = that width.
 int gemm_bf16_2cta_launch(gb200_ctx *ctx, const void *A, int64_t lda, const void *B, int64_t ldb,
-                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream) {
+                          void *C, int64_t ldc, int64_t M, int64_t N, int64_t K, cudaStream_t stream,
+                          int tile_n_hint) {
     using namespace gemm2;
+    const int tile_n = tile_n_hint == 224 || tile_n_hint == 256 ? tile_n_hint : pick_pair_tile_n(M, N, ctx->sm_count);
     CUtensorMap ta, tb;
     int rc = get_tmap_2d(ctx, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                          (uint64_t)lda * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &ta);
     if (rc) return rc;
     rc = get_tmap_2d(ctx, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N,
-                     (uint64_t)ldb * 2, BK, HALF, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
+                     (uint64_t)ldb * 2, BK, tile_n / 2, CU_TENSOR_MAP_SWIZZLE_128B, &tb);
     if (rc) return rc;
-    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int64_t n_tiles = ((M + BM - 1) / BM) * ((N + tile_n - 1) / tile_n);
     int64_t pairs = ctx->sm_count / 2;
     if (pairs > n_tiles) pairs = n_tiles;
-    rc = ensure_dynamic_smem(ctx, gemm_bf16_2cta_kernel<0>, SMEM_BYTES);
+    auto kern = tile_n == 224 ? gemm_bf16_2cta_kernel<0, 224> : gemm_bf16_2cta_kernel<0, 256>;
+    rc = ensure_dynamic_smem(ctx, kern, SMEM_BYTES);
     if (rc) return rc;
-    GB200_CUDA_TRY(launch_pdl(gemm_bf16_2cta_kernel<0>, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
+    GB200_CUDA_TRY(launch_pdl(kern, dim3((unsigned)(2 * pairs)), dim3(NUM_THREADS),
                               (size_t)SMEM_BYTES, stream, ta, tb, static_cast<__nv_bfloat16 *>(C), ldc, (int)M,
                               (int)N, (int)K, ctx->d_status, Gemm2F32{}));
     return after_launch(ctx, "gemm_bf16_2cta_kernel");

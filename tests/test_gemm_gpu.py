@@ -202,12 +202,13 @@ def test_bf16_split_k(ctx, oracle, mnk, splits):
     assert torch.equal(c, c2)
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5, 6])
 @pytest.mark.parametrize("mnk", [(256, 256, 64), (512, 768, 1024), (300, 500, 200), (130, 258, 136), (1, 8, 8),
                                  (1024, 1280, 512), (1000, 3000, 328)])
 def test_bf16_kernel_variants(ctx, oracle, mnk, variant):
-    """Single-CTA 128x256 tiles (1), CTA-pair 256x256 tiles (2), single-CTA tiles of 192 (3) and
-    128 (4) columns, forced, ragged shapes included."""
+    """Single-CTA 128x256 tiles (1), CTA-pair tiles with the width picked (2), single-CTA tiles of 192
+    (3) and 128 (4) columns, CTA-pair tiles of 224 (5) and 256 (6) columns, forced, ragged shapes
+    included."""
     m, n, k = mnk
     g = torch.Generator(device="cuda").manual_seed(m * 3 + n * 5 + k)
     a = (torch.randn((m, k), generator=g, device="cuda") * 0.02).to(torch.bfloat16)
